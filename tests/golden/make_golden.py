@@ -1,0 +1,239 @@
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Run once, in a container that has the OneComp v1.4.0 source tree, as
+
+    python tests/golden/make_golden.py /path/to/OneCompression
+
+It imports the reference's own functions (with three third-party module roots
+that are absent here - lm_eval, ortools, primefac - replaced by inert stubs;
+none of them is touched by the path), runs them on small seeded inputs on CPU
+and stores inputs and outputs as ``.npz``.  The tests never need the reference:
+they read only the ``.npz`` files.
+"""
+
+from __future__ import annotations
+
+import importlib.abc
+import importlib.machinery
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+_STUB_ROOTS = ("lm_eval", "ortools", "primefac")
+
+
+class _Stub(types.ModuleType):
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return _Stub(self.__name__ + "." + name)
+
+    def __call__(self, *a, **k):
+        return _Stub(self.__name__ + "()")
+
+
+class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    def find_spec(self, fullname, path, target=None):
+        if fullname.split(".")[0] in _STUB_ROOTS:
+            return importlib.machinery.ModuleSpec(fullname, self, is_package=True)
+        return None
+
+    def create_module(self, spec):
+        m = _Stub(spec.name)
+        m.__path__ = []
+        return m
+
+    def exec_module(self, module):
+        pass
+
+
+def _import_reference(root):
+    sys.meta_path.insert(0, _Finder())
+    sys.path.insert(0, root)
+
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _np(t):
+    if t is None:
+        return np.zeros((0,), dtype=np.int64)
+    if t.dtype == torch.float16:
+        return t.numpy().view(np.uint16)  # stored as raw bits
+    return t.numpy()
+
+
+def synth_layer(seed, out, d, ntok, outliers=4, dead=()):
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(out, d, generator=g) * 0.02).half()
+    x = torch.randn(ntok, d, generator=g)
+    idx = torch.randperm(d, generator=g)[:outliers]
+    x[:, idx] *= 20
+    for c in dead:
+        x[:, c] = 0
+    return w, x.half()
+
+
+# (name, out, d, ntok, kwargs)
+GPTQ_CASES = [
+    ("b4_g128_asym", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=False)),
+    ("b3_g128_sym", 32, 256, 1024, dict(wbits=3, groupsize=128, sym=True)),
+    ("b4_g32_asym_stale", 32, 256, 1024, dict(wbits=4, groupsize=32, sym=False)),
+    ("b2_g64_asym", 32, 256, 1024, dict(wbits=2, groupsize=64, sym=False)),
+    ("b8_perchannel_sym", 32, 256, 1024, dict(wbits=8, groupsize=-1, sym=True)),
+    ("b4_perchannel_asym", 32, 256, 1024, dict(wbits=4, groupsize=-1, sym=False)),
+    ("b4_g128_asym_actorder", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=False, actorder=True)),
+    ("b3_g128_sym_actorder", 32, 256, 1024, dict(wbits=3, groupsize=128, sym=True, actorder=True)),
+    ("b4_g32_ragged_d160", 32, 160, 640, dict(wbits=4, groupsize=32, sym=False)),
+    ("b4_g128_dead", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=False, _dead=(3, 130))),
+    ("b4_g128_block64", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=True, blocksize=64)),
+]
+
+
+def main(ref_root):
+    _import_reference(ref_root)
+    from onecomp.quantizer.gptq import _gptq as ref_gptq
+    from onecomp.quantizer.gptq import gptq_layer as ref_layer
+    from onecomp.qep import _quantize_with_qep_arch as ref_arch
+
+    torch.set_num_threads(1)
+
+    # ---- packing -----------------------------------------------------------
+    pack = {}
+    g = torch.Generator().manual_seed(11)
+    for bits in (2, 3, 4, 8):
+        codes = torch.randint(0, 2**bits, (64, 96), generator=g, dtype=torch.int32)
+        zeros = torch.randint(0, 2**bits, (3, 64), generator=g, dtype=torch.int32)
+        zeros[0, :4] = 0  # stored value becomes -1 and must be masked
+        pack[f"codes{bits}"] = codes.numpy()
+        pack[f"zeros{bits}"] = zeros.numpy()
+        pack[f"qweight{bits}"] = ref_layer.pack_int_weights(codes, bits).numpy()
+        pack[f"qzeros{bits}"] = ref_layer.pack_zeros(zeros - 1, bits).numpy()
+        pack[f"unpacked{bits}"] = ref_layer.unpack_int_weights(
+            ref_layer.pack_int_weights(codes, bits), bits, (64, 96)
+        ).numpy()
+    np.savez_compressed(os.path.join(HERE, "pack.npz"), **pack)
+
+    # ---- find_params ---------------------------------------------------------
+    fp = {}
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(24, 40, generator=g) * 0.05
+    x[0] = 0  # all-zero row
+    x[1] = x[1].abs()  # minimum clipped to 0
+    x[2] = -x[2].abs()  # maximum clipped to 0
+    x[3, 0] = 0.7  # outlier
+    fp["x"] = x.numpy()
+    for bits in (2, 3, 4, 8):
+        for sym in (False, True):
+            ex = ref_gptq.GPTQExcecutor()
+            ex.configure(bits, perchannel=True, sym=sym, mse=False)
+            ex.find_params(x.clone(), weight=True)
+            fp[f"scale_b{bits}_s{int(sym)}"] = ex.scale.numpy()
+            fp[f"zero_b{bits}_s{int(sym)}"] = ex.zero.numpy()
+            q = ref_gptq.quantize(x, ex.scale, ex.zero, ex.maxq)
+            fp[f"q_b{bits}_s{int(sym)}"] = q.numpy()
+            fp[f"dq_b{bits}_s{int(sym)}"] = ref_gptq.dequantize(q, ex.scale, ex.zero, ex.maxq).numpy()
+    ex = ref_gptq.GPTQExcecutor()
+    ex.configure(4, perchannel=True, sym=False, mse=True, norm=2.4, grid=100)
+    ex.find_params(x.clone(), weight=True)
+    fp["scale_mse"] = ex.scale.numpy()
+    fp["zero_mse"] = ex.zero.numpy()
+    np.savez_compressed(os.path.join(HERE, "find_params.npz"), **fp)
+
+    # ---- moments ---------------------------------------------------------------
+    mom = {}
+    g = torch.Generator().manual_seed(13)
+    xq = (torch.randn(20, 16, 64, generator=g)).half()  # 20 seqs -> slices of 8,8,4
+    xf = (xq.float() * (1 + 0.03 * torch.randn(20, 16, 64, generator=g))).half()
+    lin = torch.nn.Linear(64, 8, bias=False).half()
+    qz = ref_gptq.GPTQ(wbits=4, groupsize=-1)
+    h, n = qz.calculate_hessian(lin, xq)
+    mom.update(xq=_np(xq), xf=_np(xf), H=h.numpy(), n=np.int64(n))
+    mom["C_generic"] = qz.calculate_delta_hatX(lin, xq, xf).numpy()
+
+    class _Blk(torch.nn.Module):
+        def __init__(self, lin):
+            super().__init__()
+            self.lin = lin
+
+        def forward(self, x, **kw):
+            return self.lin(x)
+
+    bq, bf = _Blk(torch.nn.Linear(64, 8, bias=False).half()), _Blk(torch.nn.Linear(64, 8, bias=False).half())
+    hh, cc, nn_ = ref_arch.compute_hessian_and_crossterm(
+        bq, bf, bq.lin, bf.lin, xq, xf, {}, 6, torch.device("cpu")
+    )
+    mom.update(H_arch=hh.numpy(), C_arch=cc.numpy(), n_arch=np.int64(nn_), arch_chunk=np.int64(6))
+    np.savez_compressed(os.path.join(HERE, "moments.npz"), **mom)
+
+    # ---- run_gptq / quantize_layer / dequantize ----------------------------------
+    for k, (name, out, d, ntok, kw) in enumerate(GPTQ_CASES):
+        kw = dict(kw)
+        dead = kw.pop("_dead", ())
+        w, x = synth_layer(100 + k, out, d, ntok, dead=dead)
+        lin = torch.nn.Linear(d, out, bias=False).half()
+        lin.weight.data = w.clone()
+        blocksize = kw.pop("blocksize", 128)
+        qz = ref_gptq.GPTQ(blocksize=blocksize, **kw)
+        qz.module_to_name = {lin: "layer"}
+        h, n = qz.calculate_hessian(lin, x.unsqueeze(0))
+        raw = ref_gptq.run_gptq(
+            h.clone(), lin, blocksize=blocksize, percdamp=0.01, wbits=kw["wbits"],
+            groupsize=kw["groupsize"], actorder=kw.get("actorder", False), mse=False,
+            sym=kw["sym"],
+        )
+        u = ref_gptq._compute_inverse_hessian(_prep_h(h.clone(), raw["perm"]), 0.01)
+        res = qz.quantize_layer(lin, None, hessian=h.clone())
+        deq = res.compute_dequantized_weight()
+        np.savez_compressed(
+            os.path.join(HERE, f"gptq_{name}.npz"),
+            W=_np(w), H=h.numpy(), n=np.int64(n), blocksize=np.int64(blocksize),
+            wbits=np.int64(kw["wbits"]), groupsize=np.int64(kw["groupsize"]),
+            sym=np.int64(kw["sym"]), actorder=np.int64(kw.get("actorder", False)),
+            codes=raw["qweight"].numpy(), scales=_np(raw["scales"]), qzeros=raw["qzeros"].numpy(),
+            perm=_np(raw["perm"]), U=u.numpy(),
+            qweight_packed=res.qweight.numpy(), qzeros_packed=res.qzeros.numpy(),
+            dequantized=_np(deq),
+        )
+
+    # ---- QEP weight correction -----------------------------------------------------
+    w, x = synth_layer(300, 32, 128, 1024)
+    g = torch.Generator().manual_seed(301)
+    xq = (x.float() * (1 + 0.05 * torch.randn(x.shape, generator=g))).half()
+    lin = torch.nn.Linear(128, 32, bias=False).half()
+    lin.weight.data = w.clone()
+    qz = ref_gptq.GPTQ(wbits=4, groupsize=128, sym=False)
+    qz.module_to_name = {lin: "layer"}
+    h, n = qz.calculate_hessian(lin, xq.unsqueeze(0))
+    c = qz.calculate_delta_hatX(lin, xq.unsqueeze(0), x.unsqueeze(0))
+    qz.adjust_weight(lin, None, None, original_hessian=h, original_delta_hatX=c,
+                     percdamp=0.01, perccorr=0.5)
+    adjusted = lin.weight.data.clone()
+    lin.weight.data = w.clone()
+    qz.quantize_with_qep(lin, None, None, percdamp=0.01, perccorr=0.5,
+                         hessian=h.clone(), delta_hatX=c.clone())
+    res = qz.results["layer"]
+    np.savez_compressed(
+        os.path.join(HERE, "qep_adjust.npz"),
+        W=_np(w), H=h.numpy(), C=c.numpy(), n=np.int64(n), adjusted=_np(adjusted),
+        qweight_packed=res.qweight.numpy(), qzeros_packed=res.qzeros.numpy(),
+        scales=_np(res.scales), dequantized=_np(res.compute_dequantized_weight()),
+    )
+    print("golden fixtures written to", HERE)
+
+
+def _prep_h(h, perm):
+    dead = torch.diag(h) == 0
+    h[dead, dead] = 1
+    if perm is not None:
+        h = h[perm][:, perm]
+    return h
+
+
+if __name__ == "__main__":
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the OneCompression source tree>")
+    main(sys.argv[1])
