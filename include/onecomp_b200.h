@@ -1,0 +1,154 @@
+/*
+ * C ABI of libonecomp_b200.so: hand-written sm_100a kernels for the GPTQ / QEP
+ * layer-quantization path of OneComp (v1.4.0).
+ *
+ * OneComp exposes no FFI for this path; its boundary is the Python quantizer
+ * protocol (GPTQ.quantize_layer, Quantizer.calculate_hessian / adjust_weight,
+ * compute_hessian_and_crossterm, pack_int_weights ...).  Each entry point
+ * below replaces the torch call sites named in its comment (paths are relative
+ * to the OneComp source tree) and is what a binding for that call site would
+ * bind.  Conventions:
+ *
+ *   - plain pointers and sizes only; every pointer is DEVICE memory unless it
+ *     says otherwise; matrices are row-major with an explicit leading dimension
+ *     in elements;
+ *   - nothing here allocates: scratch is passed in, its size comes from the
+ *     matching *_workspace_bytes function;
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*);
+ *   - the return value is 0 on success or a negative OC_ERR_* code, with a
+ *     message available from oc_last_error() (per host thread);
+ *   - `status` words are device ints written by the kernels (0 = fine); the
+ *     caller reads them after synchronising.
+ */
+#ifndef ONECOMP_B200_H
+#define ONECOMP_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OC_OK 0
+#define OC_ERR_INVALID_ARG (-1)
+#define OC_ERR_CUDA (-2)
+#define OC_ERR_UNSUPPORTED (-3)
+#define OC_ERR_WORKSPACE (-4)
+#define OC_ERR_TOO_LARGE (-5)
+
+int oc_version(void);
+const char* oc_last_error(void);
+
+/* ---- second moments -------------------------------------------------------
+ * H <- a_old*H + a_new * Xq^T Xq   and, when C != NULL,
+ * C <- a_old*C + a_new * (Xf - Xq)^T Xq,   X* = [n_tok, d] fp16 (ld elements), H, C = [d, d] fp32.
+ *
+ * Replaces the fp32 cast + scale + SGEMM of Quantizer.calculate_hessian
+ * (onecomp/quantizer/_quantizer.py:811-830), calculate_delta_hatX (:869-893),
+ * compute_hessian_and_crossterm (onecomp/qep/_quantize_with_qep_arch.py:182-196)
+ * and _compute_per_module_hessians (:252-262).  The running mean of the
+ * reference is a_old = n/(n+t), a_new = 2/(n+t).
+ *
+ * Tensor-core path (tcgen05 + TMA): taken when d, ld are multiples of 8, ldh of 4,
+ * pointers 16-byte aligned, n_tok > 0, status != NULL and (for C) delta_scratch
+ * ([n_tok, ld] fp16) is given.  It writes only the tiles of H that touch the upper
+ * triangle: call oc_mirror_upper(H) once after the last accumulation.  C is
+ * written in full.  Any other shape runs an fp32 FMA kernel that writes H in full.
+ * chunk_tokens (0 = 2048): tokens per tensor-core accumulation chain.
+ * sm_count: CTAs to launch at most (0 = 148).  force_simt: 1 selects the FMA kernel.
+ * status: 0, or 101..104 when a bounded pipeline wait expired (result invalid).
+ */
+int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok, int d,
+                    long long ld, float* H, float* C, long long ldh, float a_old, float a_new,
+                    int chunk_tokens, int sm_count, int force_simt, int* status, void* stream);
+
+/* lower triangle <- upper triangle */
+int oc_mirror_upper(float* M, long long ld, int n, void* stream);
+
+/* ---- inverse-Hessian factor -------------------------------------------------
+ * U upper triangular, U^T U = (P Hfix P^T + shift I)^-1 where Hfix is H with 1 on
+ * dead diagonals (H[j][j] == 0), shift = rel_shift * percdamp * mean(diag Hfix), and
+ * P sorts columns by descending diagonal when actorder != 0 (stable; identity
+ * otherwise).  Replaces run_gptq's dead-column fix, argsort and gathers
+ * (onecomp/quantizer/gptq/_gptq.py:693-702) and _compute_inverse_hessian
+ * (:594-643: damping, cholesky, cholesky_inverse, cholesky upper) with one blocked
+ * Cholesky factorisation and one triangular inverse.  H is not modified.
+ *
+ * Outputs: U [n,n] (ldu), perm/invperm int32 [n], dead uint8 [n] (original column
+ * order), damp_out float[2] = {percdamp*mean, mean}, status int = 0 or (index+1) of
+ * the first non-positive pivot (then U is meaningless: add damping and call again,
+ * as the reference's retry loop does; reuse_perm = 1 keeps perm/invperm).
+ */
+long long oc_hinv_workspace_bytes(int n);
+int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float rel_shift,
+                   int actorder, int reuse_perm, float* U, long long ldu, int* perm, int* invperm,
+                   unsigned char* dead, float* damp_out, int* status, void* workspace,
+                   long long workspace_bytes, void* stream);
+
+/* ---- GPTQ column loop ---------------------------------------------------------
+ * Quantizes W [out, d] fp16 (ldw) given U from oc_hinv_factor.  Replaces run_gptq's
+ * float conversion, per-channel fit, dead-column zeroing, act-order gather, the
+ * per-column loop with group fitting (find_params), the lazy-batch trailing update
+ * and the inverse permutation (onecomp/quantizer/gptq/_gptq.py:678-768, 800-840,
+ * 886-926), plus the packing of GPTQ.quantize_layer (:445-464; layout
+ * onecomp/quantizer/gptq/gptq_layer.py:36-83) and the dequantised weight used for
+ * propagation (:153-168).
+ *
+ * perm / invperm / dead may be NULL (no act-order / no dead columns).
+ * blocksize 1..128.  groupsize -1 (per channel) or >= 1; G = 1 or ceil(d/groupsize).
+ * Outputs, each optional (NULL skips it); ld_out is the row count of the whole
+ * layer when `out` is a row slab of it (pass pointers already offset to the slab;
+ * slabs must start on multiples of 32 rows), else `out`:
+ *   qweight  int32 [d*bits/32, ld_out]   packed codes, original column order
+ *   qzeros   int32 [G, ld_out*bits/32]   packed (zero - 1) & mask
+ *   scales16 fp16  [G, ld_out]
+ *   scales32 fp32  [G, ld_out]           scales before the fp16 cast
+ *   zeros    int32 [G, ld_out]           raw zero points
+ *   codes    int32 [out, d]              unpacked codes, original column order
+ *   w_hat    fp16  [out, d] (ldwh)       fp16( float(fp16 scale) * (code - zero) )
+ */
+long long oc_gptq_workspace_bytes(int out, int d, int groupsize);
+int oc_gptq_quantize(const void* W, long long ldw, int out, int d, const float* U, long long ldu,
+                     const int* perm, const int* invperm, const unsigned char* dead, int wbits,
+                     int groupsize, int sym, int blocksize, int sm_count, int* qweight, int* qzeros,
+                     void* scales16, float* scales32, int* zeros, long long ld_out, int* codes,
+                     void* w_hat, long long ldwh, void* workspace, long long workspace_bytes,
+                     void* stream);
+
+/* ---- QEP weight correction ------------------------------------------------------
+ * W <- fp16( Wz + perccorr * (Wz C) (P^T U^T U P) ), Wz = W with dead columns zeroed,
+ * in place on W [out, d] fp16.  Replaces Quantizer.adjust_weight's SGEMM, potrf and
+ * potrs (onecomp/quantizer/_quantizer.py:398-432) given the factor of the same damped
+ * Hessian.  out <= 65535 per call.
+ */
+long long oc_qep_workspace_bytes(int out, int d);
+int oc_qep_adjust(void* W, long long ldw, int out, int d, const float* C, long long ldc,
+                  const float* U, long long ldu, const int* perm, const unsigned char* dead,
+                  float perccorr, void* workspace, long long workspace_bytes, void* stream);
+
+/* ---- packed-layout utilities (onecomp/quantizer/gptq/gptq_layer.py:36-170) --------
+ * pack_int_weights / unpack_int_weights: codes int32 [out, d] <-> qweight int32
+ * [d*bits/32, out].  pack_zeros / unpack_zeros: zeros int32 [G, out] <-> qzeros int32
+ * [G, out*bits/32]; `add` is added before masking (-1 stores the v1 offset, +1
+ * restores it).  bits in {2, 3, 4, 8}.
+ */
+int oc_pack_qweight(const int* codes, int out, int d, int bits, int* qweight, void* stream);
+int oc_unpack_qweight(const int* qweight, int out, int d, int bits, int* codes, void* stream);
+int oc_pack_qzeros(const int* zeros, int G, int out, int bits, int add, int* qzeros, void* stream);
+int oc_unpack_qzeros(const int* qzeros, int G, int out, int bits, int add, int* zeros, void* stream);
+
+/* GPTQResult.compute_dequantized_weight (onecomp/quantizer/gptq/_gptq.py:84-168) on a
+ * packed result: w16[r][c] = fp16( float(scales16[g_idx[c]][r]) * (q - ((stored zero + 1) & mask)) ).
+ * g_idx int32 [d] (NULL = one group). */
+int oc_dequantize_packed(const int* qweight, const int* qzeros, const void* scales16,
+                         const int* g_idx, int out, int d, int bits, void* w16, long long ldw,
+                         void* stream);
+
+/* fp32 GEMM engine: C = beta*C + alpha*opA(A)*opB(B); transX = 1 means the operand is
+ * stored transposed ([K,M] / [N,K]); flags: see OC_GEMM_* in csrc/common.cuh (0 = dense). */
+int oc_gemm_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
+                long long ldc, int M, int N, int K, float alpha, float beta, int transA,
+                int transB, int flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

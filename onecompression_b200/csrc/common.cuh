@@ -1,0 +1,68 @@
+// Shared helpers for the sm_100a kernels of the GPTQ / QEP path.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+// Status codes returned by every extern "C" entry point.
+#define OC_OK 0
+#define OC_ERR_INVALID_ARG (-1)
+#define OC_ERR_CUDA (-2)
+#define OC_ERR_UNSUPPORTED (-3)
+#define OC_ERR_WORKSPACE (-4)
+#define OC_ERR_TOO_LARGE (-5)
+
+#define OC_CHECK_LAUNCH()                                   \
+  do {                                                      \
+    cudaError_t e__ = cudaGetLastError();                   \
+    if (e__ != cudaSuccess) {                               \
+      oc_set_last_error(cudaGetErrorString(e__));           \
+      return OC_ERR_CUDA;                                   \
+    }                                                       \
+  } while (0)
+
+#define OC_CUDA(call)                                       \
+  do {                                                      \
+    cudaError_t e__ = (call);                               \
+    if (e__ != cudaSuccess) {                               \
+      oc_set_last_error(cudaGetErrorString(e__));           \
+      return OC_ERR_CUDA;                                   \
+    }                                                       \
+  } while (0)
+
+#define OC_REQUIRE(cond, msg)                               \
+  do {                                                      \
+    if (!(cond)) {                                          \
+      oc_set_last_error(msg);                               \
+      return OC_ERR_INVALID_ARG;                            \
+    }                                                       \
+  } while (0)
+
+void oc_set_last_error(const char* msg);
+
+static inline int oc_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---- fp32 GEMM engine (gemm.cu) -------------------------------------------
+// C[M,N] = beta*C + alpha * opA(A) * opB(B), all fp32, exact FMA arithmetic.
+//   transA = 0: A is [M,K] row-major (lda);  1: A is [K,M] row-major.
+//   transB = 0: B is [K,N] row-major (ldb);  1: B is [N,K] row-major.
+// Flags restrict work to the structurally non-zero part of triangular
+// operands; coordinates are relative to the sub-matrices passed in.
+enum : int {
+  OC_GEMM_SKIP_UPPER_TILES = 1,  // do not compute tiles entirely above the diagonal of C
+  OC_GEMM_KLO_FROM_N = 2,        // op(B)[k,n] == 0 for k < n   (k range starts at tile's first n)
+  OC_GEMM_KHI_FROM_M = 4,        // op(A)[m,k] == 0 for k > m   (k range ends at tile's last m)
+  OC_GEMM_KHI_FROM_N = 8,        // op(B)[k,n] == 0 for k > n   (k range ends at tile's last n)
+  OC_GEMM_KLO_FROM_M = 16,       // op(A)[m,k] == 0 for k < m   (k range starts at tile's first m)
+};
+
+struct OcGemm {
+  const float* A; long long lda; long long strideA;
+  const float* B; long long ldb; long long strideB;
+  float* C; long long ldc; long long strideC;
+  int M, N, K;
+  float alpha, beta;
+  int transA, transB, flags, batch;
+};
+
+int oc_gemm_f32_launch(const OcGemm& g, cudaStream_t stream);

@@ -1,0 +1,277 @@
+// Inverse-Hessian factor for GPTQ: U upper triangular with U^T U = (H + damp I)^-1.
+//
+// Replaces the potrf + potri + potrf sequence of the reference
+// (onecomp/quantizer/gptq/_gptq.py:594-643, call sites :693-706) with one
+// Cholesky factorisation and one triangular inverse:
+//
+//   A = J (P H P^T + damp I) J      (J reverses the index order, P is the act-order permutation)
+//   A = L L^T                       blocked right-looking Cholesky, fp32
+//   X = L^-1                        recursive blocked triangular inverse, fp32
+//   U = J X J                       upper triangular, U^T U = (P H P^T + damp I)^-1
+//
+// because J L J is the upper factor V of H = V V^T and U = V^-1.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NB = 128;  // panel width
+
+// ---- diag statistics: dead columns, damping --------------------------------
+// diagv[j] = H[j,j] (1 where it is 0), dead[j], damp_out[0] = percdamp * mean(diagv)
+__global__ void diag_stats_kernel(const float* __restrict__ H, long long ld, int n, float percdamp,
+                                  float* __restrict__ diagv, unsigned char* __restrict__ dead,
+                                  float* __restrict__ damp_out) {
+  __shared__ double red[32];
+  double s = 0.0;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    float v = H[(long long)j * ld + j];
+    const bool dd = (v == 0.f);
+    if (dd) v = 1.f;
+    diagv[j] = v;
+    dead[j] = dd ? 1 : 0;
+    s += (double)v;
+  }
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) t += red[w];
+    damp_out[0] = percdamp * (float)(t / (double)n);
+    damp_out[1] = (float)(t / (double)n);
+  }
+}
+
+// ---- act-order: stable descending argsort by counting ranks ---------------------
+__global__ void rank_sort_kernel(const float* __restrict__ key, int n, int* __restrict__ perm) {
+  __shared__ float tile[1024];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const float ki = (i < n) ? key[i] : 0.f;
+  int rank = 0;
+  for (int base = 0; base < n; base += 1024) {
+    for (int t = threadIdx.x; t < 1024; t += blockDim.x) tile[t] = (base + t < n) ? key[base + t] : 0.f;
+    __syncthreads();
+    const int lim = min(1024, n - base);
+    for (int t = 0; t < lim; ++t) {
+      const float kj = tile[t];
+      const int j = base + t;
+      rank += (kj > ki || (kj == ki && j < i)) ? 1 : 0;
+    }
+    __syncthreads();
+  }
+  if (i < n) perm[rank] = i;
+}
+
+__global__ void iota_kernel(int* __restrict__ perm, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) perm[i] = i;
+}
+
+__global__ void invert_perm_kernel(const int* __restrict__ perm, int* __restrict__ inv, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) inv[perm[i]] = i;
+}
+
+// ---- A = J (P Hfix P^T + shift I) J ------------------------------------------------
+__global__ void build_reversed_kernel(const float* __restrict__ H, long long ldh, int n,
+                                      const int* __restrict__ perm, const float* __restrict__ diagv,
+                                      const float* __restrict__ damp, float rel_shift,
+                                      float* __restrict__ A, long long lda) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = blockIdx.y;
+  if (j >= n) return;
+  const int pi = perm[n - 1 - i], pj = perm[n - 1 - j];
+  float v;
+  if (i == j) v = diagv[pi] + rel_shift * damp[0];
+  else v = H[(long long)pi * ldh + pj];
+  A[(long long)i * lda + j] = v;
+}
+
+// ---- U = J X J (upper part), zero below the diagonal ------------------------------------
+__global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx, int n,
+                                     float* __restrict__ U, long long ldu) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int i = blockIdx.y;
+  if (j >= n) return;
+  U[(long long)i * ldu + j] = (j >= i) ? X[(long long)(n - 1 - i) * ldx + (n - 1 - j)] : 0.f;
+}
+
+// ---- one diagonal block: Cholesky in shared memory, then its inverse ---------------------
+// A block (nb x nb, lower part read) -> L written back over the lower part;
+// L^-1 written to the matching block of X (lower part; upper part zero).
+// A non-positive or non-finite pivot records (global index + 1) in *status (first one wins)
+// and continues with pivot 1 so that every later kernel still terminates.
+__global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
+                                                         float* __restrict__ X, long long ldx,
+                                                         int k0, int nb, int* __restrict__ status) {
+  extern __shared__ float sm[];
+  float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);
+  float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));
+  const int tid = threadIdx.x;
+  float* Ab = A + (long long)k0 * lda + k0;
+  float* Xb = X + (long long)k0 * ldx + k0;
+  for (int e = tid; e < NB * NB; e += blockDim.x) {
+    const int i = e / NB, j = e % NB;
+    S[i][j] = (i < nb && j <= i) ? Ab[(long long)i * lda + j] : ((i == j) ? 1.f : 0.f);
+  }
+  __syncthreads();
+  for (int j = 0; j < nb; ++j) {
+    if (tid == 0) {
+      float p = S[j][j];
+      if (!(p > 0.f) || !isfinite(p)) {
+        atomicCAS(status, 0, k0 + j + 1);
+        p = 1.f;
+      }
+      S[j][j] = sqrtf(p);
+    }
+    __syncthreads();
+    const float inv = 1.f / S[j][j];
+    for (int i = j + 1 + tid; i < nb; i += blockDim.x) S[i][j] *= inv;
+    __syncthreads();
+    // trailing lower update: S[i][k] -= S[i][j] * S[k][j],  j < k <= i < nb
+    const int m = nb - j - 1;
+    for (int e = tid; e < m * m; e += blockDim.x) {
+      const int i = j + 1 + e / m, k = j + 1 + e % m;
+      if (k <= i) S[i][k] = fmaf(-S[i][j], S[k][j], S[i][k]);
+    }
+    __syncthreads();
+  }
+  // inverse by forward substitution, one column per thread
+  if (tid < NB) {
+    const int c = tid;
+    for (int i = 0; i < NB; ++i) Y[i][c] = 0.f;
+    if (c < nb) {
+      Y[c][c] = 1.f / S[c][c];
+      for (int i = c + 1; i < nb; ++i) {
+        float acc = 0.f;
+        for (int k = c; k < i; ++k) acc = fmaf(S[i][k], Y[k][c], acc);
+        Y[i][c] = -acc / S[i][i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < nb * nb; e += blockDim.x) {
+    const int i = e / nb, j = e % nb;
+    if (j <= i) Ab[(long long)i * lda + j] = S[i][j];
+    Xb[(long long)i * ldx + j] = (j <= i) ? Y[i][j] : 0.f;
+  }
+}
+
+}  // namespace
+
+// Workspace layout (floats): A[n*ld] | X[n*ld] | T[n*ld] | diagv[n] | damp[4];  ld = round_up(n,4)
+static long long factor_ws_floats(int n) {
+  const long long ld = (n + 3) / 4 * 4;
+  return 3 * (long long)n * ld + ((n + 3) / 4 * 4) + 4;
+}
+
+extern "C" long long oc_hinv_workspace_bytes(int n) {
+  return factor_ws_floats(n) * 4 + (long long)((n + 3) / 4 * 4);  // + dead bytes
+}
+
+// See include/onecomp_b200.h for the contract.
+extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float rel_shift,
+                              int actorder, int reuse_perm, float* U, long long ldu, int* perm,
+                              int* invperm, unsigned char* dead, float* damp_out, int* status,
+                              void* workspace, long long workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  OC_REQUIRE(H && U && perm && invperm && dead && damp_out && status && workspace, "hinv_factor: null pointer");
+  OC_REQUIRE(n > 0 && ldh >= n && ldu >= n, "hinv_factor: bad dimensions");
+  if (workspace_bytes < oc_hinv_workspace_bytes(n)) {
+    oc_set_last_error("hinv_factor: workspace too small");
+    return OC_ERR_WORKSPACE;
+  }
+  const long long ld = (n + 3) / 4 * 4;
+  float* A = (float*)workspace;
+  float* X = A + (long long)n * ld;
+  float* T = X + (long long)n * ld;
+  float* diagv = T + (long long)n * ld;
+
+  OC_CUDA(cudaMemsetAsync(status, 0, sizeof(int), stream));
+  diag_stats_kernel<<<1, 1024, 0, stream>>>(H, ldh, n, percdamp, diagv, dead, damp_out);
+  OC_CHECK_LAUNCH();
+  const int tb = 256, gb = oc_div_up(n, tb);
+  if (!reuse_perm) {
+    if (actorder) rank_sort_kernel<<<gb, tb, 0, stream>>>(diagv, n, perm);
+    else iota_kernel<<<gb, tb, 0, stream>>>(perm, n);
+    OC_CHECK_LAUNCH();
+    invert_perm_kernel<<<gb, tb, 0, stream>>>(perm, invperm, n);
+    OC_CHECK_LAUNCH();
+  }
+  build_reversed_kernel<<<dim3(gb, n), tb, 0, stream>>>(H, ldh, n, perm, diagv, damp_out, rel_shift, A, ld);
+  OC_CHECK_LAUNCH();
+  OC_CUDA(cudaMemsetAsync(X, 0, (size_t)n * ld * sizeof(float), stream));
+
+  // ---- blocked right-looking Cholesky --------------------------------------------------
+  static bool attr_set = false;
+  const int smem = 2 * NB * (NB + 1) * (int)sizeof(float);
+  if (!attr_set) {
+    OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  for (int k0 = 0; k0 < n; k0 += NB) {
+    const int nb = min(NB, n - k0);
+    potrf_diag_kernel<<<1, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status);
+    OC_CHECK_LAUNCH();
+    const int rest = n - k0 - nb;
+    if (rest <= 0) break;
+    float* panel = A + (long long)(k0 + nb) * ld + k0;
+    OcGemm g{};
+    // panel <- panel * (Lkk^-1)^T  (in place: one column tile, every CTA reads its rows first)
+    g.A = panel; g.lda = ld; g.B = X + (long long)k0 * ld + k0; g.ldb = ld; g.C = panel; g.ldc = ld;
+    g.M = rest; g.N = nb; g.K = nb; g.alpha = 1.f; g.beta = 0.f; g.transA = 0; g.transB = 1;
+    g.flags = 0; g.batch = 1;
+    int rc = oc_gemm_f32_launch(g, stream);
+    if (rc) return rc;
+    // trailing <- trailing - panel * panel^T  (lower tiles only)
+    OcGemm s{};
+    s.A = panel; s.lda = ld; s.B = panel; s.ldb = ld;
+    s.C = A + (long long)(k0 + nb) * ld + (k0 + nb); s.ldc = ld;
+    s.M = rest; s.N = rest; s.K = nb; s.alpha = -1.f; s.beta = 1.f; s.transA = 0; s.transB = 1;
+    s.flags = OC_GEMM_SKIP_UPPER_TILES; s.batch = 1;
+    rc = oc_gemm_f32_launch(s, stream);
+    if (rc) return rc;
+  }
+
+  // ---- recursive blocked inverse of L: X holds the inverted diagonal blocks -----------------
+  for (long long s = NB; s < n; s *= 2) {
+    const int nprob = (int)((n + 2 * s - 1) / (2 * s));
+    int nfull = 0;
+    for (int m = 0; m < nprob; ++m) {
+      const long long mid = 2 * s * m + s, end = 2 * s * m + 2 * s;
+      if (mid < n && end <= n) nfull = m + 1;
+    }
+    for (int pass = 0; pass < 2; ++pass) {
+      // pass 0: the uniform problems as one batch; pass 1: a ragged last problem, if any
+      int first, count, rows = 0;
+      if (pass == 0) { first = 0; count = nfull; rows = (int)s; }
+      else {
+        first = nfull; count = 0;
+        const long long mid = 2 * s * first + s;
+        if (first < nprob && mid < n) { count = 1; rows = (int)(n - mid); }
+      }
+      if (count == 0) continue;
+      const long long r0 = 2 * s * first, mid = r0 + s;
+      const long long stride = 2 * s * (ld + 1);
+      OcGemm g1{};  // T21 = L21 * X11   (X11 lower triangular)
+      g1.A = A + mid * ld + r0; g1.lda = ld; g1.strideA = stride;
+      g1.B = X + r0 * ld + r0; g1.ldb = ld; g1.strideB = stride;
+      g1.C = T + mid * ld + r0; g1.ldc = ld; g1.strideC = stride;
+      g1.M = rows; g1.N = (int)s; g1.K = (int)s; g1.alpha = 1.f; g1.beta = 0.f;
+      g1.flags = OC_GEMM_KLO_FROM_N; g1.batch = count;
+      int rc = oc_gemm_f32_launch(g1, stream);
+      if (rc) return rc;
+      OcGemm g2{};  // X21 = -X22 * T21  (X22 lower triangular)
+      g2.A = X + mid * ld + mid; g2.lda = ld; g2.strideA = stride;
+      g2.B = T + mid * ld + r0; g2.ldb = ld; g2.strideB = stride;
+      g2.C = X + mid * ld + r0; g2.ldc = ld; g2.strideC = stride;
+      g2.M = rows; g2.N = (int)s; g2.K = rows; g2.alpha = -1.f; g2.beta = 0.f;
+      g2.flags = OC_GEMM_KHI_FROM_M; g2.batch = count;
+      rc = oc_gemm_f32_launch(g2, stream);
+      if (rc) return rc;
+    }
+  }
+  reverse_upper_kernel<<<dim3(gb, n), tb, 0, stream>>>(X, ld, n, U, ldu);
+  OC_CHECK_LAUNCH();
+  return OC_OK;
+}

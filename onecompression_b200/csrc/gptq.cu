@@ -1,0 +1,412 @@
+// GPTQ column loop for one Linear weight, given the inverse-Hessian factor U.
+//
+// Follows run_gptq of the reference (onecomp/quantizer/gptq/_gptq.py:646-794)
+// operation for operation in fp32: true divides, round-half-to-even, the
+// rank-1 update as a rounded product followed by a rounded subtraction (this
+// file is compiled with -fmad=false and uses the _rn intrinsics besides).
+//
+// Rows of W are independent given U, so one thread owns one row for a whole
+// block of up to 128 columns: the row's block lives in shared memory, 32
+// columns at a time in registers; the in-block error propagation needs no
+// inter-thread communication at all.  The lazy-batch trailing update
+// W[:, i2:] -= Err * U[i1:i2, i2:] is a launch of the fp32 GEMM engine with
+// the error block stored transposed (coalesced stores here, coalesced loads
+// there).  Codes are kept transposed ([column][row], 16 bit) until a final
+// pass packs them in original column order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLK = 128;      // maximum GPTQ block size handled by the column kernel
+constexpr int SUB = 32;       // columns held in registers at a time
+constexpr int WS = BLK + 4;   // shared tile row stride in floats (odd multiple of 16 bytes)
+
+struct ColArgs {
+  const float* Wf; long long ldw;
+  int out, d, i1, count;
+  const float* U; long long ldu;
+  float* ErrT; long long lde;
+  unsigned short* codesT;
+  float* scales; float* zeros;  // [G][out] fp32 (G = 1 for per-channel)
+  int gs, maxq, sym;
+};
+
+// scale / zero over the values v[0..n), reference: GPTQExcecutor.find_params
+// (onecomp/quantizer/gptq/_gptq.py:886-972, perchannel=True, mse=False)
+__device__ __forceinline__ void params_from_range(float mn, float mx, int maxq, int sym,
+                                                  float& scale, float& zero) {
+  // mn <= 0 <= mx on entry
+  if (sym) {
+    mx = fmaxf(fabsf(mn), mx);
+    if (mn < 0.f) mn = -mx;
+  }
+  if (mn == 0.f && mx == 0.f) { mn = -1.f; mx = 1.f; }
+  scale = __fdiv_rn(__fsub_rn(mx, mn), (float)maxq);
+  zero = sym ? (float)(maxq + 1) * 0.5f : rintf(__fdiv_rn(-mn, scale));
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gptq_block_kernel(ColArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  float* Us = sm;               // [BLK][BLK], upper triangle of the diagonal block of U
+  float* Ws = sm + BLK * BLK;   // [WARPS*32][WS], block-entry values of the rows' columns
+  constexpr int NTHR = WARPS * 32;
+  const int tid = threadIdx.x;
+  const int row0 = blockIdx.x * NTHR;
+  const int count = a.count, i1 = a.i1;
+
+  for (int e = tid; e < BLK * BLK; e += NTHR) {
+    const int i = e / BLK, j = e % BLK;
+    Us[e] = (i < count && j < count && j >= i) ? a.U[(long long)(i1 + i) * a.ldu + i1 + j] : 0.f;
+  }
+  for (int e = tid; e < NTHR * BLK; e += NTHR) {
+    const int r = e / BLK, c = e % BLK;
+    Ws[r * WS + c] = (row0 + r < a.out && c < count) ? a.Wf[(long long)(row0 + r) * a.ldw + i1 + c] : 0.f;
+  }
+  __syncthreads();
+
+  const int row = row0 + tid;
+  if (row >= a.out) return;
+  float* wrow = Ws + tid * WS;
+  const float* grow = a.Wf + (long long)row * a.ldw;  // block-entry state of the whole row
+  const float maxqf = (float)a.maxq;
+  const int gs = a.gs;
+  float scale, zero;
+  if (gs == -1) { scale = a.scales[row]; zero = a.zeros[row]; }
+  else { scale = 1.f; zero = 0.f; }
+
+  for (int cb = 0; cb < count; cb += SUB) {
+    float w[SUB], er[SUB];
+#pragma unroll
+    for (int v = 0; v < SUB / 4; ++v) {
+      const float4 t = *reinterpret_cast<const float4*>(wrow + cb + 4 * v);
+      w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+    }
+#pragma unroll
+    for (int i = 0; i < SUB; ++i) {
+      const int ci = cb + i;
+      er[i] = 0.f;
+      if (ci < count) {
+        const int col = i1 + ci;
+        if (gs != -1 && col % gs == 0) {
+          // Group parameters are fitted on the block-entry values of columns
+          // col .. col+gs-1 (reference :737-745 reads the matrix, not the block copy).
+          const int n = min(gs, a.d - col);
+          float mn = 0.f, mx = 0.f;
+          if (ci == 0 && n <= count) {
+            for (int t = 0; t < n; ++t) { const float v = wrow[t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
+          } else {
+            for (int t = 0; t < n; ++t) { const float v = grow[col + t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
+          }
+          params_from_range(mn, mx, a.maxq, a.sym, scale, zero);
+          const int g = col / gs;
+          a.scales[(long long)g * a.out + row] = scale;
+          a.zeros[(long long)g * a.out + row] = zero;
+        }
+        const float x = w[i];
+        float q = __fadd_rn(rintf(__fdiv_rn(x, scale)), zero);
+        q = fminf(fmaxf(q, 0.f), maxqf);
+        const float dq = __fmul_rn(scale, __fsub_rn(q, zero));
+        const float e = __fdiv_rn(__fsub_rn(x, dq), Us[ci * BLK + ci]);
+        er[i] = e;
+        a.codesT[(long long)col * a.out + row] = (unsigned short)q;
+        a.ErrT[(long long)ci * a.lde + row] = e;
+        const float4* up = reinterpret_cast<const float4*>(Us + ci * BLK + cb);
+#pragma unroll
+        for (int j4 = (i + 1) / 4; j4 < SUB / 4; ++j4) {
+          const float4 u = up[j4];
+          if (4 * j4 + 0 > i) w[4 * j4 + 0] = __fsub_rn(w[4 * j4 + 0], __fmul_rn(e, u.x));
+          if (4 * j4 + 1 > i) w[4 * j4 + 1] = __fsub_rn(w[4 * j4 + 1], __fmul_rn(e, u.y));
+          if (4 * j4 + 2 > i) w[4 * j4 + 2] = __fsub_rn(w[4 * j4 + 2], __fmul_rn(e, u.z));
+          if (4 * j4 + 3 > i) w[4 * j4 + 3] = __fsub_rn(w[4 * j4 + 3], __fmul_rn(e, u.w));
+        }
+      }
+    }
+    // Later columns of the block receive this sub-block's 32 updates now, in the
+    // same order (ascending source column) and with the same two roundings each.
+    for (int jc = cb + SUB; jc < count; jc += 8) {
+      float4 t0 = *reinterpret_cast<const float4*>(wrow + jc);
+      float4 t1 = *reinterpret_cast<const float4*>(wrow + jc + 4);
+#pragma unroll
+      for (int i = 0; i < SUB; ++i) {
+        const float e = er[i];
+        const float4 u0 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc);
+        const float4 u1 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc + 4);
+        t0.x = __fsub_rn(t0.x, __fmul_rn(e, u0.x)); t0.y = __fsub_rn(t0.y, __fmul_rn(e, u0.y));
+        t0.z = __fsub_rn(t0.z, __fmul_rn(e, u0.z)); t0.w = __fsub_rn(t0.w, __fmul_rn(e, u0.w));
+        t1.x = __fsub_rn(t1.x, __fmul_rn(e, u1.x)); t1.y = __fsub_rn(t1.y, __fmul_rn(e, u1.y));
+        t1.z = __fsub_rn(t1.z, __fmul_rn(e, u1.z)); t1.w = __fsub_rn(t1.w, __fmul_rn(e, u1.w));
+      }
+      *reinterpret_cast<float4*>(wrow + jc) = t0;
+      *reinterpret_cast<float4*>(wrow + jc + 4) = t1;
+    }
+  }
+}
+
+// ---- preparation: fp16 -> fp32, act-order gather, dead columns, per-channel parameters ----
+// Wf[r][j] = dead[perm[j]] ? 0 : float(W[r][perm[j]]).  Per-channel scale / zero are fitted on
+// the whole original row before dead columns are zeroed (reference :690-695).
+__global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_in, int out, int d,
+                                    const int* __restrict__ perm, const unsigned char* __restrict__ dead,
+                                    float* __restrict__ Wf, long long ldw, int per_channel, int maxq,
+                                    int sym, float* __restrict__ scales, float* __restrict__ zeros) {
+  const int row = blockIdx.x;
+  const __half* src = W + (long long)row * ldw_in;
+  float* dst = Wf + (long long)row * ldw;
+  float mn = 0.f, mx = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    const int pj = perm ? perm[j] : j;
+    const float v = __half2float(src[pj]);
+    mn = fminf(mn, v); mx = fmaxf(mx, v);
+    dst[j] = (dead && dead[pj]) ? 0.f : v;
+  }
+  if (!per_channel) return;
+  __shared__ float smn[32], smx[32];
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) { smn[threadIdx.x >> 5] = mn; smx[threadIdx.x >> 5] = mx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x + 31) / 32; ++w) { mn = fminf(mn, smn[w]); mx = fmaxf(mx, smx[w]); }
+    float s, z;
+    params_from_range(mn, mx, maxq, sym, s, z);
+    scales[row] = s;
+    zeros[row] = z;
+  }
+}
+
+// ---- final pass: pack, cast, dequantize ---------------------------------------------------
+// Packed layout: pack_int_weights / pack_zeros of the reference
+// (onecomp/quantizer/gptq/gptq_layer.py:36-83, 129-139, 160-170).
+__device__ __forceinline__ void pack3(const unsigned (&v)[32], unsigned (&w)[3]) {
+  w[0] = w[1] = w[2] = 0u;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    const int bit = 3 * k, wi = bit >> 5, off = bit & 31;
+    w[wi] |= v[k] << off;
+    if (off + 3 > 32) w[wi + 1] |= v[k] >> (32 - off);
+  }
+}
+
+// qweight[pr][r]: codes of original columns pr*f .. pr*f+f-1 (3 bit: 32 columns -> 3 words)
+__global__ void pack_qweight_kernel(const unsigned short* __restrict__ codesT, int out, int d,
+                                    const int* __restrict__ invperm, int bits,
+                                    int* __restrict__ qweight, long long ldq) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= out) return;
+  const unsigned mask = (1u << bits) - 1u;
+  if (bits == 3) {
+    const int c0 = blockIdx.y * 32;
+    unsigned v[32], w[3];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const int c = c0 + k;
+      const int j = invperm ? invperm[c] : c;
+      v[k] = codesT[(long long)j * out + r] & mask;
+    }
+    pack3(v, w);
+#pragma unroll
+    for (int t = 0; t < 3; ++t) qweight[(long long)(blockIdx.y * 3 + t) * ldq + r] = (int)w[t];
+  } else {
+    const int f = 32 / bits;
+    const int c0 = blockIdx.y * f;
+    unsigned word = 0u;
+    for (int k = 0; k < f; ++k) {
+      const int c = c0 + k;
+      const int j = invperm ? invperm[c] : c;
+      word |= ((unsigned)codesT[(long long)j * out + r] & mask) << (k * bits);
+    }
+    qweight[(long long)blockIdx.y * ldq + r] = (int)word;
+  }
+}
+
+// qzeros[g][w]: (zero - 1) & mask of rows w*f .. w*f+f-1 (3 bit: 32 rows -> 3 words)
+__global__ void pack_qzeros_kernel(const float* __restrict__ zeros, int out, int G, int bits,
+                                   int* __restrict__ qzeros, long long ldz) {
+  const int g = blockIdx.y;
+  const unsigned mask = (1u << bits) - 1u;
+  const float* zr = zeros + (long long)g * out;
+  if (bits == 3) {
+    const int blk = blockIdx.x * blockDim.x + threadIdx.x;
+    if (blk * 32 >= out) return;
+    unsigned v[32], w[3];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = (unsigned)((int)zr[blk * 32 + k] - 1) & mask;
+    pack3(v, w);
+#pragma unroll
+    for (int t = 0; t < 3; ++t) qzeros[(long long)g * ldz + blk * 3 + t] = (int)w[t];
+  } else {
+    const int f = 32 / bits;
+    const int wi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (wi * f >= out) return;
+    unsigned word = 0u;
+    for (int k = 0; k < f; ++k) word |= ((unsigned)((int)zr[wi * f + k] - 1) & mask) << (k * bits);
+    qzeros[(long long)g * ldz + wi] = (int)word;
+  }
+}
+
+__global__ void cast_params_kernel(const float* __restrict__ scales, const float* __restrict__ zeros,
+                                   int out, int G, __half* __restrict__ scales16, long long lds,
+                                   float* __restrict__ scales32, int* __restrict__ zeros_i32) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int g = blockIdx.y;
+  if (r >= out) return;
+  const float s = scales[(long long)g * out + r];
+  if (scales16) scales16[(long long)g * lds + r] = __float2half_rn(s);
+  if (scales32) scales32[(long long)g * lds + r] = s;
+  if (zeros_i32) zeros_i32[(long long)g * lds + r] = (int)zeros[(long long)g * out + r];
+}
+
+// Original-order outputs through a 32x32 transpose: integer codes [out][d] and the fp16
+// dequantised weight  fp16( float(fp16(scale)) * (q - zero) )  (reference :153-168).
+__global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ codesT, int out, int d,
+                                         const int* __restrict__ invperm, int gs,
+                                         const float* __restrict__ scales, const float* __restrict__ zeros,
+                                         int* __restrict__ codes, long long ldc,
+                                         __half* __restrict__ what, long long ldwh) {
+  __shared__ unsigned short tq[32][33];
+  __shared__ float tv[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+  for (int k = ty; k < 32; k += 8) {
+    const int c = c0 + k, r = r0 + tx;
+    if (c < d && r < out) {
+      const int j = invperm ? invperm[c] : c;
+      const int g = (gs == -1) ? 0 : j / gs;
+      const unsigned short q = codesT[(long long)j * out + r];
+      tq[k][tx] = q;
+      const float s = __half2float(__float2half_rn(scales[(long long)g * out + r]));
+      tv[k][tx] = __fmul_rn(s, __fsub_rn((float)q, zeros[(long long)g * out + r]));
+    }
+  }
+  __syncthreads();
+  for (int k = ty; k < 32; k += 8) {
+    const int r = r0 + k, c = c0 + tx;
+    if (c < d && r < out) {
+      if (codes) codes[(long long)r * ldc + c] = (int)tq[tx][k];
+      if (what) what[(long long)r * ldwh + c] = __float2half_rn(tv[tx][k]);
+    }
+  }
+}
+
+template <int WARPS>
+int launch_block(const ColArgs& a, cudaStream_t stream) {
+  static bool attr_set = false;
+  const int smem = (BLK * BLK + WARPS * 32 * WS) * (int)sizeof(float);
+  if (!attr_set) {
+    OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  gptq_block_kernel<WARPS><<<oc_div_up(a.out, WARPS * 32), WARPS * 32, smem, stream>>>(a);
+  OC_CHECK_LAUNCH();
+  return OC_OK;
+}
+
+long long round4(long long x) { return (x + 3) / 4 * 4; }
+
+}  // namespace
+
+extern "C" long long oc_gptq_workspace_bytes(int out, int d, int groupsize) {
+  const long long G = (groupsize == -1) ? 1 : (d + groupsize - 1) / groupsize;
+  long long b = 0;
+  b += (long long)out * round4(d) * 4;       // Wf
+  b += (long long)BLK * round4(out) * 4;     // ErrT
+  b += round4((long long)d * out * 2);       // codesT
+  b += 2 * G * (long long)out * 4;           // scales, zeros fp32
+  return b + 256;
+}
+
+// See include/onecomp_b200.h for the contract.
+extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d, const float* U,
+                                long long ldu, const int* perm, const int* invperm,
+                                const unsigned char* dead, int wbits, int groupsize, int sym,
+                                int blocksize, int sm_count, int* qweight, int* qzeros, void* scales16_,
+                                float* scales32, int* zeros_i32, long long ld_out, int* codes,
+                                void* what_, long long ldwh, void* workspace,
+                                long long workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const __half* W = (const __half*)W_;
+  __half* scales16 = (__half*)scales16_;
+  __half* what = (__half*)what_;
+  OC_REQUIRE(W && U && workspace, "gptq_quantize: null pointer");
+  OC_REQUIRE(out > 0 && d > 0 && ldw_in >= d && ldu >= d, "gptq_quantize: bad dimensions");
+  OC_REQUIRE(wbits >= 1 && wbits <= 15, "gptq_quantize: wbits must be in 1..15");
+  OC_REQUIRE(groupsize == -1 || groupsize >= 1, "gptq_quantize: groupsize must be -1 or >= 1");
+  if (blocksize < 1 || blocksize > BLK) {
+    oc_set_last_error("gptq_quantize: blocksize must be in 1..128");
+    return OC_ERR_UNSUPPORTED;
+  }
+  if (qweight || qzeros) {
+    OC_REQUIRE(wbits == 2 || wbits == 3 || wbits == 4 || wbits == 8, "gptq_quantize: packing needs wbits in {2,3,4,8}");
+    const int f = (wbits == 3) ? 32 : 32 / wbits;
+    if (qweight) OC_REQUIRE(d % f == 0, "gptq_quantize: in_features not divisible by the pack factor");
+    if (qzeros) OC_REQUIRE(out % f == 0 && ld_out % f == 0, "gptq_quantize: out_features not divisible by the pack factor");
+  }
+  if (workspace_bytes < oc_gptq_workspace_bytes(out, d, groupsize)) {
+    oc_set_last_error("gptq_quantize: workspace too small");
+    return OC_ERR_WORKSPACE;
+  }
+  if (ld_out < out) ld_out = out;
+  const int G = (groupsize == -1) ? 1 : (d + groupsize - 1) / groupsize;
+  const long long ldw = round4(d), lde = round4(out);
+  char* ws = (char*)workspace;
+  float* Wf = (float*)ws;                      ws += (long long)out * ldw * 4;
+  float* ErrT = (float*)ws;                    ws += (long long)BLK * lde * 4;
+  unsigned short* codesT = (unsigned short*)ws; ws += round4((long long)d * out * 2);
+  float* scales = (float*)ws;                  ws += (long long)G * out * 4;
+  float* zeros = (float*)ws;
+  const int maxq = (1 << wbits) - 1;
+
+  gptq_prepare_kernel<<<out, 256, 0, stream>>>(W, ldw_in, out, d, perm, dead, Wf, ldw,
+                                               groupsize == -1 ? 1 : 0, maxq, sym, scales, zeros);
+  OC_CHECK_LAUNCH();
+
+  if (sm_count <= 0) sm_count = 148;
+  const int warps_total = oc_div_up(out, 32);
+  const int per_sm = oc_div_up(warps_total, sm_count);
+  for (int i1 = 0; i1 < d; i1 += blocksize) {
+    const int count = min(blocksize, d - i1);
+    ColArgs a{Wf, ldw, out, d, i1, count, U, ldu, ErrT, lde, codesT, scales, zeros, groupsize, maxq, sym};
+    int rc;
+    if (per_sm <= 1) rc = launch_block<1>(a, stream);
+    else if (per_sm <= 2) rc = launch_block<2>(a, stream);
+    else if (per_sm <= 4) rc = launch_block<4>(a, stream);
+    else rc = launch_block<8>(a, stream);
+    if (rc) return rc;
+    const int i2 = i1 + count;
+    if (i2 < d) {
+      OcGemm g{};
+      g.A = ErrT; g.lda = lde; g.transA = 1;
+      g.B = U + (long long)i1 * ldu + i2; g.ldb = ldu; g.transB = 0;
+      g.C = Wf + i2; g.ldc = ldw;
+      g.M = out; g.N = d - i2; g.K = count; g.alpha = -1.f; g.beta = 1.f; g.flags = 0; g.batch = 1;
+      rc = oc_gemm_f32_launch(g, stream);
+      if (rc) return rc;
+    }
+  }
+
+  const int tb = 128;
+  if (qweight) {
+    const int prow = (wbits == 3) ? d / 32 : d / (32 / wbits);
+    pack_qweight_kernel<<<dim3(oc_div_up(out, tb), prow), tb, 0, stream>>>(codesT, out, d, invperm, wbits, qweight, ld_out);
+    OC_CHECK_LAUNCH();
+  }
+  if (qzeros) {
+    const int f = (wbits == 3) ? 32 : 32 / wbits;
+    const long long ldz = (wbits == 3) ? ld_out / 32 * 3 : ld_out / f;
+    pack_qzeros_kernel<<<dim3(oc_div_up(out / f, tb), G), tb, 0, stream>>>(zeros, out, G, wbits, qzeros, ldz);
+    OC_CHECK_LAUNCH();
+  }
+  if (scales16 || scales32 || zeros_i32) {
+    cast_params_kernel<<<dim3(oc_div_up(out, tb), G), tb, 0, stream>>>(scales, zeros, out, G, scales16, ld_out, scales32, zeros_i32);
+    OC_CHECK_LAUNCH();
+  }
+  if (codes || what) {
+    unpermute_outputs_kernel<<<dim3(oc_div_up(d, 32), oc_div_up(out, 32)), dim3(32, 8), 0, stream>>>(
+        codesT, out, d, invperm, groupsize, scales, zeros, codes, d, what, ldwh);
+    OC_CHECK_LAUNCH();
+  }
+  return OC_OK;
+}

@@ -1,0 +1,435 @@
+"""Tensor-level wrappers over the C ABI (``include/onecomp_b200.h``).
+
+torch supplies device memory and the current stream; all arithmetic happens in
+the CUDA library.  Nothing here falls back to torch or to the CPU: a missing
+library or a CPU tensor raises.
+"""
+
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import call, ptr, stream_handle
+
+logger = logging.getLogger(__name__)
+
+PACKABLE_WBITS = (2, 3, 4, 8)
+MAX_BLOCKSIZE = 128
+
+_sm_count_cache: dict[int, int] = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _sm_count_cache:
+        _sm_count_cache[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count_cache[idx]
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{what} must be a CUDA tensor: onecompression_b200 runs on the GPU only (no CPU path)"
+        )
+
+
+# ---------------------------------------------------------------------------
+# second moments
+# ---------------------------------------------------------------------------
+
+
+class MomentAccumulator:
+    """Running-mean Hessian H = (2/N) XqᵀXq and, optionally, the QEP cross term
+    C = (2/N)(Xf − Xq)ᵀXq, accumulated chunk by chunk on the GPU.
+
+    Same update rule as the reference (onecomp/quantizer/_quantizer.py:824-830,
+    onecomp/qep/_quantize_with_qep_arch.py:182-196): before a chunk of t tokens
+    the moments are scaled by n/(n+t), then the chunk enters with weight 2/(n+t).
+    """
+
+    def __init__(self, d: int, device, cross: bool = False, chunk_tokens: int = 0,
+                 force_simt: bool = False):
+        self.d = d
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("MomentAccumulator needs a CUDA device (no CPU path)")
+        self.H = torch.zeros((d, d), dtype=torch.float32, device=self.device)
+        self.C = torch.zeros((d, d), dtype=torch.float32, device=self.device) if cross else None
+        self.nsamples = 0
+        self.chunk_tokens = chunk_tokens
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the tensor-core kernel needs 16-byte rows; decide once so that every chunk of
+        # one accumulation takes the same path
+        self.force_simt = bool(force_simt) or d % 8 != 0
+        self._scratch = None
+        self._needs_mirror = False
+
+    def add(self, xq: torch.Tensor, xf: Optional[torch.Tensor] = None):
+        """Fold a chunk of activations ([..., d], fp16) into the moments."""
+        if xq.shape[-1] != self.d:
+            raise ValueError(f"activation width {xq.shape[-1]} != {self.d}")
+        xq = self._as_rows(xq)
+        t = xq.shape[0]
+        if t == 0:
+            return
+        cross = self.C is not None
+        if cross:
+            if xf is None:
+                raise ValueError("this accumulator also builds the cross term: pass xf")
+            xf = self._as_rows(xf)
+            if xf.shape != xq.shape:
+                raise ValueError("xf and xq differ in shape")
+        n = self.nsamples
+        a_old = n / (n + t)
+        a_new = 2.0 / (n + t)
+        self.nsamples = n + t
+        scratch = None
+        if cross and not self.force_simt:
+            if self._scratch is None or self._scratch.numel() < xq.numel():
+                self._scratch = torch.empty(xq.numel(), dtype=torch.float16, device=self.device)
+            scratch = self._scratch
+        with torch.cuda.device(self.device):
+            call(
+                "oc_moment_accum", ptr(xq), ptr(xf) if cross else None, ptr(scratch), t, self.d,
+                xq.stride(0), ptr(self.H), ptr(self.C), self.d, a_old, a_new, self.chunk_tokens,
+                sm_count(self.device), 1 if self.force_simt else 0, ptr(self.status), stream_handle(),
+            )
+        self._needs_mirror = not self.force_simt
+
+    def _as_rows(self, x: torch.Tensor) -> torch.Tensor:
+        _require_cuda(x, "activations")
+        if x.dtype != torch.float16:
+            x = x.to(torch.float16)
+        x = x.reshape(-1, self.d)
+        if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+            x = x.contiguous()
+        return x
+
+    def finalize(self, check: bool = True):
+        """Complete H (mirror the upper triangle) and return (H, C, nsamples)."""
+        if self._needs_mirror:
+            with torch.cuda.device(self.device):
+                call("oc_mirror_upper", ptr(self.H), self.d, self.d, stream_handle())
+            self._needs_mirror = False
+        if check:
+            code = int(self.status.item())
+            if code != 0:
+                raise RuntimeError(f"moment kernel: a bounded pipeline wait expired (code {code})")
+        self._scratch = None
+        return self.H, self.C, self.nsamples
+
+
+def hessian_from_activations(x: torch.Tensor, seqs_per_slice: int = 8, **kw):
+    """(H, N) for activations [batch, seq, d], folding ``seqs_per_slice`` sequences at a
+    time as Quantizer.calculate_hessian does (onecomp/quantizer/_quantizer.py:811-830)."""
+    if x.dim() == 2:
+        x = x.unsqueeze(0)
+    acc = MomentAccumulator(x.shape[-1], x.device, cross=False, **kw)
+    step = min(x.shape[0], seqs_per_slice)
+    for s in range(0, x.shape[0], step):
+        acc.add(x[s : s + step])
+    h, _, n = acc.finalize()
+    return h, n
+
+
+# ---------------------------------------------------------------------------
+# inverse-Hessian factor
+# ---------------------------------------------------------------------------
+
+
+@dataclass
+class HessianFactor:
+    """U with UᵀU = (P H Pᵀ + damp·I)⁻¹ plus what the column loop needs with it."""
+
+    u: torch.Tensor            # [d, d] fp32, upper triangular
+    perm: torch.Tensor         # int32 [d]
+    invperm: torch.Tensor      # int32 [d]
+    dead: torch.Tensor         # uint8 [d], original column order
+    damp: torch.Tensor         # float32 [2]: percdamp*mean(diag), mean(diag)
+    actorder: bool
+    percdamp: float
+    rel_shift: float           # multiple of damp that was added to the diagonal
+    attempts: int
+
+
+_ws_cache: dict = {}
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    """A reusable scratch buffer per device (grown on demand)."""
+    key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _ws_cache.pop(key, None)
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def release_workspaces():
+    _ws_cache.clear()
+
+
+def factor_hessian(h: torch.Tensor, percdamp: float, actorder: bool, max_retries: int = 5,
+                   shifts=None) -> HessianFactor:
+    """Factor a Hessian for GPTQ with the reference's retry rule: when the Cholesky
+    factorisation meets a non-positive pivot, 10ᵏ·damp more is added to the diagonal
+    (k = 1, 2, …) and it is tried again, ``max_retries`` attempts in all
+    (onecomp/quantizer/gptq/_gptq.py:618-641).  ``h`` is not modified.
+
+    ``shifts`` optionally gives the diagonal shift of each attempt as a multiple of
+    damp (used by the QEP correction, whose rule differs on retries).
+    """
+    _require_cuda(h, "hessian")
+    if h.dtype != torch.float32:
+        h = h.float()
+    if h.stride(1) != 1:
+        h = h.contiguous()
+    d = h.shape[0]
+    dev = h.device
+    u = torch.empty((d, d), dtype=torch.float32, device=dev)
+    perm = torch.empty(d, dtype=torch.int32, device=dev)
+    invperm = torch.empty(d, dtype=torch.int32, device=dev)
+    dead = torch.empty(d, dtype=torch.uint8, device=dev)
+    damp = torch.empty(2, dtype=torch.float32, device=dev)
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        nbytes = _lib.load().oc_hinv_workspace_bytes(d)
+        ws = _workspace(nbytes, dev)
+        rel, mult = 1.0, 1.0
+        for attempt in range(max_retries):
+            if shifts is not None:
+                rel = shifts(attempt, float(percdamp))
+            call(
+                "oc_hinv_factor", ptr(h), h.stride(0), d, float(percdamp), float(rel),
+                1 if actorder else 0, 1 if attempt > 0 else 0, ptr(u), d, ptr(perm), ptr(invperm),
+                ptr(dead), ptr(damp), ptr(status), ptr(ws), ws.numel(), stream_handle(),
+            )
+            if int(status.item()) == 0:
+                return HessianFactor(u, perm, invperm, dead, damp, bool(actorder), float(percdamp),
+                                     rel, attempt + 1)
+            mult *= 10.0
+            extra = mult * float(damp[0].item())
+            rel += mult
+            logger.warning(
+                "Cholesky failed (attempt %d/%d); adding extra damping %.2e",
+                attempt + 1, max_retries, extra,
+            )
+    raise RuntimeError(
+        "Cholesky decomposition failed after %d damping attempts. "
+        "The Hessian may be severely ill-conditioned." % max_retries
+    )
+
+
+# ---------------------------------------------------------------------------
+# GPTQ column loop
+# ---------------------------------------------------------------------------
+
+
+def gptq_quantize(
+    weight: torch.Tensor,
+    factor: HessianFactor,
+    wbits: int,
+    groupsize: int,
+    sym: bool,
+    blocksize: int = 128,
+    pack: bool = True,
+    want_codes: bool = False,
+    want_dequantized: bool = True,
+    want_scales_f32: bool = False,
+    outputs: Optional[dict] = None,
+    ld_out: Optional[int] = None,
+):
+    """Run the column loop on ``weight`` [out, d] fp16 (CUDA) with a ready factor.
+
+    Returns a dict of CUDA tensors: qweight / qzeros (packed, when ``pack``), scales
+    (fp16 [G, out]), zeros (int32 [G, out]), optionally codes (int32 [out, d]),
+    dequantized (fp16 [out, d]), scales_f32.  ``outputs`` may provide pre-allocated
+    views (row slabs of full-layer buffers) under the same keys together with
+    ``ld_out``, the row count of the full layer.
+    """
+    _require_cuda(weight, "weight")
+    if weight.dtype != torch.float16:
+        raise TypeError("gptq_quantize expects an fp16 weight")
+    if weight.dim() != 2:
+        raise ValueError("weight must be 2-D [out_features, in_features]")
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    out, d = weight.shape
+    dev = weight.device
+    if factor.u.shape[0] != d:
+        raise ValueError("factor and weight disagree on in_features")
+    if not 1 <= blocksize <= MAX_BLOCKSIZE:
+        raise NotImplementedError(
+            f"blocksize {blocksize}: the CUDA column kernel handles 1..{MAX_BLOCKSIZE}"
+        )
+    groups = 1 if groupsize == -1 else (d + groupsize - 1) // groupsize
+    outputs = dict(outputs or {})
+    ld = ld_out if ld_out is not None else out
+    if pack:
+        if wbits not in PACKABLE_WBITS:
+            raise ValueError(f"packing supports wbits in {PACKABLE_WBITS}; got {wbits}")
+        f = 32 if wbits == 3 else 32 // wbits
+        # same assertions (and wording) as the reference packer, gptq_layer.py:55-66
+        if wbits == 3:
+            assert d % 32 == 0, f"rows ({d}) must be divisible by 32 for 3-bit packing"
+            assert out % 32 == 0, f"rows ({out}) must be divisible by 32 for 3-bit packing"
+        else:
+            assert d % f == 0, f"rows ({d}) must be divisible by pack_factor ({f})"
+            assert out % f == 0, f"rows ({out}) must be divisible by pack_factor ({f})"
+        if "qweight" not in outputs:
+            outputs["qweight"] = torch.empty((d * wbits // 32, out), dtype=torch.int32, device=dev)
+        if "qzeros" not in outputs:
+            outputs["qzeros"] = torch.empty((groups, out * wbits // 32), dtype=torch.int32, device=dev)
+    if "scales" not in outputs:
+        outputs["scales"] = torch.empty((groups, out), dtype=torch.float16, device=dev)
+    if "zeros" not in outputs:
+        outputs["zeros"] = torch.empty((groups, out), dtype=torch.int32, device=dev)
+    if want_scales_f32 and "scales_f32" not in outputs:
+        outputs["scales_f32"] = torch.empty((groups, out), dtype=torch.float32, device=dev)
+    if want_codes and "codes" not in outputs:
+        outputs["codes"] = torch.empty((out, d), dtype=torch.int32, device=dev)
+    if want_dequantized and "dequantized" not in outputs:
+        outputs["dequantized"] = torch.empty((out, d), dtype=torch.float16, device=dev)
+    deq = outputs.get("dequantized")
+    with torch.cuda.device(dev):
+        nbytes = _lib.load().oc_gptq_workspace_bytes(out, d, groupsize)
+        ws = _workspace(nbytes, dev)
+        call(
+            "oc_gptq_quantize", ptr(weight), weight.stride(0), out, d, ptr(factor.u),
+            factor.u.stride(0), ptr(factor.perm) if factor.actorder else None,
+            ptr(factor.invperm) if factor.actorder else None, ptr(factor.dead), wbits, groupsize,
+            1 if sym else 0, blocksize, sm_count(dev), ptr(outputs.get("qweight")),
+            ptr(outputs.get("qzeros")), ptr(outputs["scales"]), ptr(outputs.get("scales_f32")),
+            ptr(outputs["zeros"]), ld, ptr(outputs.get("codes")), ptr(deq),
+            deq.stride(0) if deq is not None else d, ptr(ws), ws.numel(), stream_handle(),
+        )
+    return outputs
+
+
+# ---------------------------------------------------------------------------
+# QEP weight correction
+# ---------------------------------------------------------------------------
+
+
+def qep_adjust(weight: torch.Tensor, c: torch.Tensor, factor: HessianFactor, perccorr: float):
+    """In place: weight ← fp16(Wz + perccorr·(Wz·C)·(H+damp·I)⁻¹) for an fp16 CUDA weight."""
+    _require_cuda(weight, "weight")
+    if weight.dtype != torch.float16 or weight.dim() != 2 or weight.stride(1) != 1:
+        raise TypeError("qep_adjust expects a 2-D fp16 weight with contiguous rows")
+    if c.dtype != torch.float32 or c.stride(1) != 1:
+        c = c.float().contiguous()
+    out, d = weight.shape
+    dev = weight.device
+    with torch.cuda.device(dev):
+        for r0 in range(0, out, 65535 // 32 * 32):
+            rows = min(65535 // 32 * 32, out - r0)
+            nbytes = _lib.load().oc_qep_workspace_bytes(rows, d)
+            ws = _workspace(nbytes, dev)
+            slab = weight[r0 : r0 + rows]
+            call(
+                "oc_qep_adjust", ptr(slab), slab.stride(0), rows, d, ptr(c), c.stride(0),
+                ptr(factor.u), factor.u.stride(0), ptr(factor.perm) if factor.actorder else None,
+                ptr(factor.dead), float(perccorr), ptr(ws), ws.numel(), stream_handle(),
+            )
+    return weight
+
+
+# ---------------------------------------------------------------------------
+# packed layout utilities
+# ---------------------------------------------------------------------------
+
+
+def _pack_factor(wbits: int) -> int:
+    if wbits not in PACKABLE_WBITS:
+        raise ValueError(f"Unsupported wbits for packing: {wbits}")
+    return 32 if wbits == 3 else 32 // wbits
+
+
+def pack_qweight(codes: torch.Tensor, wbits: int) -> torch.Tensor:
+    _require_cuda(codes, "codes")
+    f = _pack_factor(wbits)
+    out, d = codes.shape
+    if wbits == 3:
+        assert d % 32 == 0, f"rows ({d}) must be divisible by 32 for 3-bit packing"
+    else:
+        assert d % f == 0, f"rows ({d}) must be divisible by pack_factor ({f})"
+    codes = codes.to(torch.int32).contiguous()
+    q = torch.empty((d * wbits // 32, out), dtype=torch.int32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        call("oc_pack_qweight", ptr(codes), out, d, wbits, ptr(q), stream_handle())
+    return q
+
+
+def unpack_qweight(qweight: torch.Tensor, wbits: int, shape) -> torch.Tensor:
+    _require_cuda(qweight, "qweight")
+    _pack_factor(wbits)
+    out, d = int(shape[0]), int(shape[1])
+    qweight = qweight.to(torch.int32).contiguous()
+    codes = torch.empty((out, d), dtype=torch.int32, device=qweight.device)
+    with torch.cuda.device(qweight.device):
+        call("oc_unpack_qweight", ptr(qweight), out, d, wbits, ptr(codes), stream_handle())
+    return codes
+
+
+def pack_qzeros(zeros: torch.Tensor, wbits: int, add: int = 0) -> torch.Tensor:
+    _require_cuda(zeros, "zeros")
+    f = _pack_factor(wbits)
+    groups, out = zeros.shape
+    if wbits == 3:
+        assert out % 32 == 0, f"rows ({out}) must be divisible by 32 for 3-bit packing"
+    else:
+        assert out % f == 0, f"rows ({out}) must be divisible by pack_factor ({f})"
+    zeros = zeros.to(torch.int32).contiguous()
+    q = torch.empty((groups, out * wbits // 32), dtype=torch.int32, device=zeros.device)
+    with torch.cuda.device(zeros.device):
+        call("oc_pack_qzeros", ptr(zeros), groups, out, wbits, add, ptr(q), stream_handle())
+    return q
+
+
+def unpack_qzeros(qzeros: torch.Tensor, wbits: int, out_features: int, add: int = 0) -> torch.Tensor:
+    _require_cuda(qzeros, "qzeros")
+    _pack_factor(wbits)
+    qzeros = qzeros.to(torch.int32).contiguous()
+    groups = qzeros.shape[0]
+    z = torch.empty((groups, out_features), dtype=torch.int32, device=qzeros.device)
+    with torch.cuda.device(qzeros.device):
+        call("oc_unpack_qzeros", ptr(qzeros), groups, out_features, wbits, add, ptr(z), stream_handle())
+    return z
+
+
+def dequantize_packed(qweight, qzeros, scales, g_idx, wbits: int, shape) -> torch.Tensor:
+    _require_cuda(qweight, "qweight")
+    out, d = int(shape[0]), int(shape[1])
+    dev = qweight.device
+    qweight = qweight.to(torch.int32).contiguous()
+    qzeros = qzeros.to(device=dev, dtype=torch.int32).contiguous()
+    scales = scales.to(device=dev, dtype=torch.float16).contiguous()
+    if g_idx is not None:
+        g_idx = g_idx.to(device=dev, dtype=torch.int32).contiguous()
+    w = torch.empty((out, d), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        call("oc_dequantize_packed", ptr(qweight), ptr(qzeros), ptr(scales), ptr(g_idx), out, d,
+             wbits, ptr(w), d, stream_handle())
+    return w
+
+
+def gemm_f32(a, b, c=None, alpha=1.0, beta=0.0, trans_a=False, trans_b=False, flags=0):
+    """fp32 GEMM engine, exposed for tests: C = beta·C + alpha·op(A)·op(B)."""
+    _require_cuda(a, "a")
+    m = a.shape[1] if trans_a else a.shape[0]
+    k = a.shape[0] if trans_a else a.shape[1]
+    n = b.shape[0] if trans_b else b.shape[1]
+    if c is None:
+        c = torch.zeros((m, n), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        call("oc_gemm_f32", ptr(a), a.stride(0), ptr(b), b.stride(0), ptr(c), c.stride(0), m, n, k,
+             float(alpha), float(beta), int(trans_a), int(trans_b), int(flags), stream_handle())
+    return c

@@ -1,0 +1,281 @@
+"""GPU parity tests of the individual kernels against the CPU oracle and the golden
+vectors produced by the reference.  Every call goes through the C ABI."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import f16, gptq_case_names, load_golden
+from oracle import gptq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from onecompression_b200 import kernels
+
+    return kernels
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+# ---- fp32 GEMM engine ------------------------------------------------------------
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (300, 260, 77), (64, 1000, 130), (513, 129, 16)])
+def test_gemm_matches_torch_fp32(K, ta, tb, m, n, k):
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randn((k, m) if ta else (m, k), generator=g)
+    b = torch.randn((n, k) if tb else (k, n), generator=g)
+    c0 = torch.randn(m, n, generator=g)
+    want = 0.5 * c0.double() - 1.5 * ((a.t() if ta else a).double() @ (b.t() if tb else b).double())
+    c = c0.clone().to(dev())
+    K.gemm_f32(a.to(dev()), b.to(dev()), c, alpha=-1.5, beta=0.5, trans_a=ta, trans_b=tb)
+    got = c.cpu().double()
+    assert ((got - want).norm() / want.norm()).item() < 2e-6
+
+
+def test_gemm_triangular_flags(K):
+    g = torch.Generator().manual_seed(5)
+    n = 384
+    low = torch.tril(torch.randn(n, n, generator=g))
+    up = torch.triu(torch.randn(n, n, generator=g))
+    a = torch.randn(200, n, generator=g)
+    # B lower triangular: k range starts at the tile's first column (flag 2)
+    got = K.gemm_f32(a.to(dev()), low.to(dev()), flags=2).cpu()
+    assert torch.allclose(got, a @ low, rtol=1e-4, atol=1e-4)
+    # B upper triangular: k range ends at the tile's last column (flag 8)
+    got = K.gemm_f32(a.to(dev()), up.to(dev()), flags=8).cpu()
+    assert torch.allclose(got, a @ up, rtol=1e-4, atol=1e-4)
+    # A lower triangular (flag 4)
+    b = torch.randn(n, 150, generator=g)
+    got = K.gemm_f32(low.to(dev()), b.to(dev()), flags=4).cpu()
+    assert torch.allclose(got, low @ b, rtol=1e-4, atol=1e-4)
+    # symmetric rank-k update, lower tiles only (flag 1)
+    p = torch.randn(n, 96, generator=g)
+    c = torch.zeros(n, n).to(dev())
+    K.gemm_f32(p.to(dev()), p.to(dev()), c, trans_b=True, flags=1)
+    want = p @ p.t()
+    assert torch.allclose(torch.tril(c.cpu()), torch.tril(want), rtol=1e-4, atol=1e-4)
+
+
+# ---- packing -------------------------------------------------------------------------
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+def test_pack_matches_reference_vectors(K, bits):
+    g = load_golden("pack.npz")
+    codes = torch.from_numpy(g[f"codes{bits}"]).to(dev())
+    zeros = torch.from_numpy(g[f"zeros{bits}"]).to(dev())
+    qw = K.pack_qweight(codes, bits)
+    assert np.array_equal(qw.cpu().numpy(), g[f"qweight{bits}"])
+    qz = K.pack_qzeros(zeros, bits, add=-1)
+    assert np.array_equal(qz.cpu().numpy(), g[f"qzeros{bits}"])
+    assert torch.equal(K.unpack_qweight(qw, bits, codes.shape), codes)
+    assert torch.equal(K.unpack_qzeros(qz, bits, zeros.shape[1], add=1), zeros)
+
+
+def test_pack_rejects_unaligned(K):
+    with pytest.raises(AssertionError):
+        K.pack_qweight(torch.zeros(8, 7, dtype=torch.int32, device=dev()), 4)
+    with pytest.raises(AssertionError):
+        K.pack_qweight(torch.zeros(8, 16, dtype=torch.int32, device=dev()), 3)
+
+
+# ---- second moments --------------------------------------------------------------------
+
+def _rel(a, b):
+    a, b = a.double(), b.double()
+    return ((a - b).norm() / b.norm()).item()
+
+
+@pytest.mark.parametrize("simt", [True, False])
+def test_moments_match_reference_vectors(K, simt):
+    g = load_golden("moments.npz")
+    xq, xf = f16(g["xq"]).to(dev()), f16(g["xf"]).to(dev())
+    acc = K.MomentAccumulator(64, dev(), cross=True, force_simt=simt)
+    chunk = int(g["arch_chunk"])
+    for a, b in zip(xq.split(chunk), xf.split(chunk)):
+        acc.add(a, b)
+    h, c, n = acc.finalize()
+    assert n == int(g["n_arch"])
+    assert _rel(h.cpu(), torch.from_numpy(g["H_arch"])) < 1e-5   # north-star tolerance for H
+    assert _rel(c.cpu(), torch.from_numpy(g["C_arch"])) < 1e-4
+    h2, n2 = K.hessian_from_activations(xq, force_simt=simt)
+    assert n2 == int(g["n"]) and _rel(h2.cpu(), torch.from_numpy(g["H"])) < 1e-5
+    assert torch.equal(h2, h2.t())
+
+
+@pytest.mark.parametrize("d,ntok,chunk", [(512, 8192, 0), (2880, 4096, 1024), (1000, 3000, 0), (264, 100, 0)])
+def test_hessian_tensor_core_vs_float64(K, d, ntok, chunk):
+    g = torch.Generator().manual_seed(d)
+    x = torch.randn(ntok, d, generator=g)
+    x[:, torch.randperm(d, generator=g)[:8]] *= 20
+    x = x.half()
+    want = (2.0 / ntok) * (x.double().t() @ x.double())
+    acc = K.MomentAccumulator(d, dev(), chunk_tokens=chunk)
+    for part in x.to(dev()).split(ntok // 2 + 7):
+        acc.add(part)
+    h, _, n = acc.finalize()
+    assert n == ntok
+    assert _rel(h.cpu(), want) < 1e-5
+    assert torch.equal(h, h.t())
+
+
+def test_cross_term_tensor_core_vs_float64(K):
+    g = torch.Generator().manual_seed(3)
+    d, ntok = 768, 4096
+    xf = torch.randn(ntok, d, generator=g).half()
+    xq = (xf.float() * (1 + 0.03 * torch.randn(ntok, d, generator=g))).half()
+    want_c = (2.0 / ntok) * ((xf.double() - xq.double()).t() @ xq.double())
+    want_h = (2.0 / ntok) * (xq.double().t() @ xq.double())
+    acc = K.MomentAccumulator(d, dev(), cross=True)
+    acc.add(xq.to(dev()), xf.to(dev()))
+    h, c, _ = acc.finalize()
+    assert _rel(h.cpu(), want_h) < 1e-5
+    assert _rel(c.cpu(), want_c) < 1e-4
+
+
+# ---- inverse-Hessian factor ---------------------------------------------------------------
+
+@pytest.mark.parametrize("name", gptq_case_names())
+def test_factor_matches_reference_u(K, name):
+    g = load_golden(f"gptq_{name}.npz")
+    h = torch.from_numpy(g["H"]).to(dev())
+    fac = K.factor_hessian(h, 0.01, bool(g["actorder"]))
+    assert fac.attempts == 1
+    if bool(g["actorder"]):
+        assert np.array_equal(fac.perm.cpu().numpy().astype(np.int64), g["perm"])
+    assert _rel(fac.u.cpu(), torch.from_numpy(g["U"])) < 2e-5
+    assert torch.equal(fac.u, torch.triu(fac.u))
+
+
+@pytest.mark.parametrize("n", [100, 129, 300, 1024])
+def test_factor_identity_property(K, n):
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(4 * n, n, generator=g)
+    h = (2.0 / (4 * n)) * (x.t() @ x)
+    fac = K.factor_hessian(h.to(dev()), 0.01, actorder=True)
+    u = fac.u.cpu().double()
+    p = fac.perm.cpu().long()
+    hp = h.double()[p][:, p] + float(fac.damp[0].item()) * torch.eye(n, dtype=torch.float64)
+    ident = u @ hp @ u.t()          # U Hp U^T = I  when U^T U = Hp^-1
+    assert (ident - torch.eye(n, dtype=torch.float64)).abs().max().item() < 5e-4
+
+
+def test_factor_retries_and_fails_like_reference(K):
+    h = -torch.eye(64)
+    with pytest.raises(RuntimeError, match="Cholesky decomposition failed after 5"):
+        K.factor_hessian(h.to(dev()), 0.01, False)
+    # PSD but rank deficient: the first damping already repairs it
+    v = torch.randn(64, 3)
+    fac = K.factor_hessian((v @ v.t()).to(dev()), 0.01, False)
+    assert fac.attempts == 1 and torch.isfinite(fac.u).all()
+    # indefinite: needs the escalating retries; diag mean 1 -> damp .01; total after k fails 0.01*(1+10+100..)
+    m = torch.eye(64)
+    m[0, 0] = -0.5
+    m[1, 1] = 2.5 - 0.0     # keeps the mean of the diagonal at about 1
+    fac = K.factor_hessian(m.to(dev()), 0.01, False)
+    assert fac.attempts == 3        # 0.01, 0.11 fail; 1.11 > 0.5 works
+
+
+# ---- column loop --------------------------------------------------------------------------------
+
+def _run_case(K, g, use_reference_u):
+    w = f16(g["W"]).to(dev())
+    bits, gs = int(g["wbits"]), int(g["groupsize"])
+    act = bool(g["actorder"])
+    h = torch.from_numpy(g["H"]).to(dev())
+    fac = K.factor_hessian(h, 0.01, act)
+    if use_reference_u:
+        fac.u = torch.from_numpy(g["U"]).to(dev()).contiguous()
+        if act:
+            perm = torch.from_numpy(g["perm"]).to(dev())
+            fac.perm = perm.to(torch.int32)
+            fac.invperm = torch.argsort(perm).to(torch.int32)
+    return K.gptq_quantize(
+        w, fac, wbits=bits, groupsize=gs, sym=bool(g["sym"]), blocksize=int(g["blocksize"]),
+        pack=True, want_codes=True, want_dequantized=True, want_scales_f32=True,
+    ), fac
+
+
+@pytest.mark.parametrize("name", gptq_case_names())
+def test_column_loop_with_reference_factor(K, name):
+    """Same U as the reference: codes, zeros and fp16 scales must agree almost everywhere
+    (the trailing fp32 GEMM sums in another order than the reference's BLAS)."""
+    g = load_golden(f"gptq_{name}.npz")
+    out, _ = _run_case(K, g, use_reference_u=True)
+    bits, gs = int(g["wbits"]), int(g["groupsize"])
+    codes = out["codes"].cpu().numpy()
+    same = (codes == g["codes"]).mean()
+    assert same >= 0.999, f"{same:.5f} identical codes"
+    zeros = out["zeros"].cpu().numpy()
+    zref = g["qzeros"] if gs != -1 else g["qzeros"].reshape(1, -1)
+    assert (zeros == zref).mean() >= 0.999
+    s = out["scales"].cpu().numpy().view(np.uint16).astype(np.int64)
+    sref = (g["scales"] if gs != -1 else g["scales"].reshape(1, -1)).astype(np.int64)
+    assert (np.abs(s - sref) <= 1).all(), "fp16 scales differ by more than one ulp"
+    if same == 1.0 and (zeros == zref).all() and (s == sref).all():
+        assert np.array_equal(out["qweight"].cpu().numpy(), g["qweight_packed"])
+        assert np.array_equal(out["qzeros"].cpu().numpy(), g["qzeros_packed"])
+        assert np.array_equal(out["dequantized"].cpu().numpy().view(np.uint16), g["dequantized"])
+
+
+@pytest.mark.parametrize("name", gptq_case_names())
+def test_full_layer_against_reference(K, name):
+    """Own factor + column loop: north-star tolerances (codes >= 99.9 %, scales 1e-3 before
+    the fp16 cast i.e. <= 1 fp16 ulp after it, reconstruction error within 0.5 %)."""
+    g = load_golden(f"gptq_{name}.npz")
+    out, fac = _run_case(K, g, use_reference_u=False)
+    bits, gs = int(g["wbits"]), int(g["groupsize"])
+    if bool(g["actorder"]):
+        assert np.array_equal(fac.perm.cpu().numpy().astype(np.int64), g["perm"])
+    codes = out["codes"].cpu().numpy()
+    assert (codes == g["codes"]).mean() >= 0.999
+    s = out["scales"].cpu().numpy().view(np.uint16).astype(np.int64)
+    sref = (g["scales"] if gs != -1 else g["scales"].reshape(1, -1)).astype(np.int64)
+    assert (np.abs(s - sref) <= 1).all()
+    # packed tensors are self-consistent with the codes (bit-exact layout)
+    qw, qz = orc.pack_result(codes, out["zeros"].cpu().numpy(), bits)
+    assert np.array_equal(out["qweight"].cpu().numpy(), qw)
+    assert np.array_equal(out["qzeros"].cpu().numpy(), qz)
+    # dequantised weight equals the reference formula applied to our own result
+    perm = fac.perm.cpu().numpy().astype(np.int64) if bool(g["actorder"]) else None
+    deq = orc.dequantize_result(qw, out["scales"].cpu(), qz, perm, bits, gs, codes.shape)
+    assert np.array_equal(out["dequantized"].cpu().numpy().view(np.uint16), deq.numpy().view(np.uint16))
+    # reconstruction error within 0.5 % of the reference's
+    w = f16(g["W"])
+    h = torch.from_numpy(g["H"])
+    e_ref = orc.reconstruction_error(w, f16(g["dequantized"]), h, int(g["n"]))
+    e_got = orc.reconstruction_error(w, out["dequantized"].cpu(), h, int(g["n"]))
+    assert abs(e_got - e_ref) <= 0.005 * e_ref
+
+
+def test_unpacked_bit_widths(K):
+    """wbits without a packed layout (here 5) still quantize; packing is refused."""
+    g = load_golden("gptq_b4_g128_asym.npz")
+    w = f16(g["W"]).to(dev())
+    fac = K.factor_hessian(torch.from_numpy(g["H"]).to(dev()), 0.01, False)
+    out = K.gptq_quantize(w, fac, wbits=5, groupsize=128, sym=False, pack=False, want_codes=True)
+    ref = orc.gptq_quantize(f16(g["W"]), torch.from_numpy(g["H"].copy()), wbits=5, groupsize=128, sym=False)
+    assert (out["codes"].cpu().numpy() == ref["qweight"].numpy()).mean() >= 0.999
+    with pytest.raises(ValueError):
+        K.gptq_quantize(w, fac, wbits=5, groupsize=128, sym=False, pack=True)
+
+
+# ---- QEP correction ---------------------------------------------------------------------------------
+
+def test_qep_adjust_matches_reference(K):
+    g = load_golden("qep_adjust.npz")
+    w = f16(g["W"]).to(dev()).contiguous()
+    h, c = torch.from_numpy(g["H"]).to(dev()), torch.from_numpy(g["C"]).to(dev())
+    for act in (False, True):
+        fac = K.factor_hessian(h, 0.01, act)
+        wa = w.clone()
+        K.qep_adjust(wa, c, fac, 0.5)
+        got = wa.cpu().numpy().view(np.uint16).astype(np.int64)
+        want = g["adjusted"].astype(np.int64)
+        assert (got == want).mean() >= 0.995          # fp16 rounding boundaries
+        assert np.abs(got - want).max() <= 1          # never more than one fp16 ulp
