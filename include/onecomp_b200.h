@@ -36,6 +36,9 @@ extern "C" {
 
 int oc_version(void);
 const char* oc_last_error(void);
+/* kernels launched by this library in the calling process so far; reset returns the old count */
+long long oc_launch_count(void);
+long long oc_launch_count_reset(void);
 
 /* ---- second moments -------------------------------------------------------
  * H <- a_old*H + a_new * Xq^T Xq   and, when C != NULL,
@@ -52,7 +55,7 @@ const char* oc_last_error(void);
  * ([n_tok, ld] fp16) is given.  It writes only the tiles of H that touch the upper
  * triangle: call oc_mirror_upper(H) once after the last accumulation.  C is
  * written in full.  Any other shape runs an fp32 FMA kernel that writes H in full.
- * chunk_tokens (0 = 2048): tokens per tensor-core accumulation chain.
+ * chunk_tokens (0 = 512): tokens per tensor-core accumulation chain.
  * sm_count: CTAs to launch at most (0 = 148).  force_simt: 1 selects the FMA kernel.
  * status: 0, or 101..104 when a bounded pipeline wait expired (result invalid).
  */

@@ -17,6 +17,8 @@ _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 SIGNATURES = {
     "oc_version": (_I, []),
     "oc_last_error": (c_char_p, []),
+    "oc_launch_count": (_L, []),
+    "oc_launch_count_reset": (_L, []),
     "oc_moment_accum": (_I, [_P, _P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _I, _P, _P]),
     "oc_mirror_upper": (_I, [_P, _L, _I, _P]),
     "oc_hinv_workspace_bytes": (_L, [_I]),

@@ -14,6 +14,7 @@
 
 #define OC_CHECK_LAUNCH()                                   \
   do {                                                      \
+    oc_count_launches(1);                                   \
     cudaError_t e__ = cudaGetLastError();                   \
     if (e__ != cudaSuccess) {                               \
       oc_set_last_error(cudaGetErrorString(e__));           \
@@ -39,6 +40,7 @@
   } while (0)
 
 void oc_set_last_error(const char* msg);
+void oc_count_launches(int n);
 
 static inline int oc_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 

@@ -1,5 +1,6 @@
 #include "common.cuh"
 #include <string.h>
+#include <atomic>
 
 static thread_local char g_last_error[256] = "";
 
@@ -11,6 +12,11 @@ void oc_set_last_error(const char* msg) {
 extern "C" const char* oc_last_error(void) { return g_last_error; }
 
 extern "C" int oc_version(void) { return 100; }
+
+static std::atomic<long long> g_launches{0};
+void oc_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+extern "C" long long oc_launch_count(void) { return g_launches.load(); }
+extern "C" long long oc_launch_count_reset(void) { return g_launches.exchange(0); }
 
 // Thin C entry over the fp32 GEMM engine (used by the host layer for the QEP
 // products and by the tests).

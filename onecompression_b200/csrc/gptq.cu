@@ -73,7 +73,11 @@ __global__ void __launch_bounds__(WARPS * 32) gptq_block_kernel(ColArgs a) {
   const int gs = a.gs;
   float scale, zero;
   if (gs == -1) { scale = a.scales[row]; zero = a.zeros[row]; }
-  else { scale = 1.f; zero = 0.f; }
+  else if (i1 % gs != 0) {
+    // the block starts inside a group opened by an earlier block: continue with its parameters
+    scale = a.scales[(long long)(i1 / gs) * a.out + row];
+    zero = a.zeros[(long long)(i1 / gs) * a.out + row];
+  } else { scale = 1.f; zero = 0.f; }
 
   for (int cb = 0; cb < count; cb += SUB) {
     float w[SUB], er[SUB];

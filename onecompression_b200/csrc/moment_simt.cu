@@ -118,6 +118,7 @@ int oc_moment_simt_launch(const __half* xq, const __half* xf, long long n_tok, i
   const int tb = 256;
   dim3 sg(oc_div_up(d, tb), d);
   if (H) scale_matrix_kernel<<<sg, tb, 0, stream>>>(H, ldh, d, a_old);
+  if (H && C) oc_count_launches(1);
   if (C) scale_matrix_kernel<<<sg, tb, 0, stream>>>(C, ldh, d, a_old);
   OC_CHECK_LAUNCH();
   if (n_tok <= 0) return OC_OK;

@@ -1,0 +1,366 @@
+"""Block-wise QEP driver (reference: onecomp/qep/_quantize_with_qep_arch.py).
+
+Per decoder block, in the reference's order: layers that share one input form a
+group; each group's Hessian H (from the block with the already quantized layers)
+and cross term C (against the full-precision block) are accumulated over the
+calibration set; every layer of the group is corrected, quantized, and replaced by
+its dequantized weight before the next group is measured; finally both blocks'
+outputs become the next block's inputs.
+
+What differs from the reference is only where time goes:
+
+* activations stay in HBM between blocks instead of travelling to the host and back;
+* the full-precision block runs once per block: the inputs of all groups are
+  captured in that pass (the reference re-runs it for every group);
+* the quantized block's passes stop at the layer whose input is being measured;
+* one inverse-Hessian factor per group serves the correction and the column loop of
+  every layer in it (the reference factors per layer, three times);
+* the cross term is not accumulated for a group none of whose layers is corrected;
+* with a process group, tokens are sharded over ranks for H and C (one all-reduce per
+  group) and weight rows are sharded over ranks for the correction and the column
+  loop (one all-gather per layer).
+"""
+
+from __future__ import annotations
+
+import copy
+from collections import OrderedDict
+from logging import getLogger
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .. import kernels
+from ..quantizer._quantizer import Quantizer
+from ..quantizer.gptq._gptq import GPTQ
+from ._qep_config import QEPConfig
+from .blockwise import (
+    StopForward, call_block, forward_input, get_blocks_and_inputs, move_to_device,
+)
+
+logger = getLogger(__name__)
+
+
+@torch.no_grad()
+def make_grouped_module(block, inps, kwargs, device):
+    """Groups of Linear modules that receive the very same input tensor object in one
+    forward of a single sample, split further by in_features (reference :47-115)."""
+    seen = []
+
+    def hook(module, inp, _out):
+        seen.append((module, inp[0] if isinstance(inp, tuple) else inp))
+
+    handles = [m.register_forward_hook(hook) for m in block.modules() if isinstance(m, nn.Linear)]
+    try:
+        call_block(block, inps[:1].to(device), kwargs)
+    finally:
+        for h in handles:
+            h.remove()
+    groups, index = [], {}
+    for module, tensor in seen:
+        key = id(tensor)
+        if key not in index:
+            index[key] = len(groups)
+            groups.append([])
+        groups[index[key]].append(module)
+    del seen
+    result = []
+    for group in groups:
+        by_dim = OrderedDict()
+        for module in group:
+            by_dim.setdefault(module.in_features, []).append(module)
+        result.extend(by_dim.values())
+    return result
+
+
+def _stop_hook(sink):
+    def pre_hook(_module, args):
+        sink(args[0] if isinstance(args, tuple) else args)
+        raise StopForward()
+
+    return pre_hook
+
+
+@torch.no_grad()
+def compute_hessian_and_crossterm(block_q, block_f, module_q, module_f, inps_q, inps_f, kwargs,
+                                  batch_size, device, dist=None):
+    """(H, C, nsamples) for one layer, running both blocks chunk by chunk
+    (reference :118-201).  Each forward stops at the measured layer."""
+    acc = kernels.MomentAccumulator(module_q.in_features, device, cross=True)
+    got = {}
+    hq = module_q.register_forward_pre_hook(_stop_hook(lambda x: got.__setitem__("q", x)))
+    hf = module_f.register_forward_pre_hook(_stop_hook(lambda x: got.__setitem__("f", x)))
+    try:
+        for first in range(0, inps_q.size(0), batch_size):
+            for blk, inps in ((block_q, inps_q), (block_f, inps_f)):
+                try:
+                    call_block(blk, inps[first : first + batch_size].to(device), kwargs)
+                except StopForward:
+                    pass
+            acc.add(got["q"], got["f"])
+    finally:
+        hq.remove()
+        hf.remove()
+    h, c, n = acc.finalize()
+    if dist is not None:
+        h, c, n = dist.reduce_moments(h, c, n)
+    return h, c, n
+
+
+@torch.no_grad()
+def _compute_per_module_hessians(block, modules, inps, kwargs, batch_size, device, dist=None):
+    """Independent Hessians of MoE expert layers from the tokens routed to each
+    (reference :204-272).  A module that saw no token maps to None."""
+    accs = {m: kernels.MomentAccumulator(m.in_features, device) for m in modules}
+    got = {}
+
+    def make(m):
+        def hook(_mod, inp, _out):
+            got[m] = inp[0] if isinstance(inp, tuple) else inp
+        return hook
+
+    handles = [m.register_forward_hook(make(m)) for m in modules]
+    try:
+        for first in range(0, inps.size(0), batch_size):
+            call_block(block, inps[first : first + batch_size].to(device), kwargs)
+            for m, x in got.items():
+                if x.numel():
+                    accs[m].add(x)
+            got.clear()
+    finally:
+        for h in handles:
+            h.remove()
+    out = {}
+    for m, acc in accs.items():
+        h, _, n = acc.finalize()
+        if dist is not None:
+            h, _, n = dist.reduce_moments(h, None, n)
+        out[m] = (h, n) if n > 0 else None
+    return out
+
+
+class BlockQuantizer:
+    """Quantizes the layers of one decoder block with error propagation."""
+
+    def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
+                 dist=None, cache_budget_bytes: Optional[int] = None):
+        self.quantizer = quantizer
+        self.cfg = qep_config
+        self.batch_size = batch_size
+        self.device = torch.device(device)
+        self.dist = dist
+        self.cache_budget_bytes = cache_budget_bytes
+
+    def _budget(self):
+        if self.cache_budget_bytes is not None:
+            return self.cache_budget_bytes
+        free, _total = torch.cuda.mem_get_info(self.device)
+        return int(free * 0.5)
+
+    @torch.no_grad()
+    def run(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None):
+        """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
+        target layers end up holding their dequantized weights."""
+        qz, dev, bs = self.quantizer, self.device, self.batch_size
+        block_f = copy.deepcopy(block_q)
+        groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
+        names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
+        mods_f = {n: m for n, m in block_f.named_modules() if isinstance(m, nn.Linear)}
+
+        regular, experts = [], []
+        for group in groups_q:
+            targets = [m for m in group if m in qz.module_to_name]
+            if not targets:
+                continue
+            if any(".experts." in qz.module_to_name[m] for m in targets):
+                experts.extend(targets)
+            else:
+                regular.append(group)
+        # experts the single-sample grouping pass never routed to (reference :436-461)
+        known = set(experts)
+        for _n, m in block_q.named_modules():
+            name = qz.module_to_name.get(m) if isinstance(m, nn.Linear) else None
+            if name is not None and ".experts." in name and m not in known:
+                experts.append(m)
+                known.add(m)
+
+        # one pass of the full-precision block: next inputs and every group's input
+        n_seq, seq = inps_f.shape[0], inps_f.shape[1]
+        need_c = []
+        for group in regular:
+            names = [qz.module_to_name[m] for m in group if m in qz.module_to_name]
+            need_c.append(any(not self._excluded(n) for n in names))
+        cache_bytes = sum(n_seq * seq * g[0].in_features * 2 for g, c in zip(regular, need_c) if c)
+        use_cache = cache_bytes <= self._budget()
+        caches = [None] * len(regular)
+        handles = []
+        cursor = {"first": 0}
+        if use_cache:
+            for gi, (group, c) in enumerate(zip(regular, need_c)):
+                if not c:
+                    continue
+                caches[gi] = torch.empty((n_seq, seq, group[0].in_features), dtype=inps_f.dtype, device=dev)
+
+                def make(gi):
+                    def pre_hook(_m, args):
+                        x = args[0] if isinstance(args, tuple) else args
+                        caches[gi][cursor["first"] : cursor["first"] + x.shape[0]].copy_(x)
+                    return pre_hook
+
+                handles.append(mods_f[names_q[group[0]]].register_forward_pre_hook(make(gi)))
+        next_f = torch.empty_like(inps_f)
+        try:
+            for first in range(0, n_seq, bs):
+                cursor["first"] = first
+                y = call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
+                next_f[first : first + bs].copy_(y)
+        finally:
+            for h in handles:
+                h.remove()
+
+        for gi, group in enumerate(regular):
+            d = group[0].in_features
+            acc = kernels.MomentAccumulator(d, dev, cross=need_c[gi])
+            cur = {}
+            hq = group[0].register_forward_pre_hook(_stop_hook(lambda x: cur.__setitem__("q", x)))
+            hf = None
+            if need_c[gi] and not use_cache:
+                hf = mods_f[names_q[group[0]]].register_forward_pre_hook(
+                    _stop_hook(lambda x: cur.__setitem__("f", x)))
+            try:
+                for first in range(0, n_seq, bs):
+                    try:
+                        call_block(block_q, inps_q[first : first + bs].to(dev), kwargs)
+                    except StopForward:
+                        pass
+                    xf = None
+                    if need_c[gi]:
+                        if use_cache:
+                            xf = caches[gi][first : first + bs]
+                        else:
+                            try:
+                                call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
+                            except StopForward:
+                                pass
+                            xf = cur["f"]
+                    acc.add(cur["q"], xf)
+            finally:
+                hq.remove()
+                if hf is not None:
+                    hf.remove()
+            caches[gi] = None
+            h, c, n = acc.finalize()
+            if self.dist is not None:
+                h, c, n = self.dist.reduce_moments(h, c, n)
+            factor = None
+            if isinstance(qz, GPTQ):
+                factor = kernels.factor_hessian(h, qz.percdamp, qz.actorder)
+            for module in group:
+                name = qz.module_to_name.get(module)
+                if name is None:
+                    continue
+                excluded = self._excluded(name)
+                self._quantize_one(module, name, h, None if excluded else c, n, factor)
+                if on_layer_done is not None:
+                    on_layer_done(f"{name}, no weight correction" if excluded else name)
+
+        if experts:
+            per_module = _compute_per_module_hessians(block_q, experts, inps_q, kwargs, bs, dev, self.dist)
+            for module in experts:
+                name = qz.module_to_name[module]
+                entry = per_module[module]
+                if entry is None:
+                    logger.warning("Expert layer %s received no tokens during calibration; skipping", name)
+                    if on_layer_done is not None:
+                        on_layer_done(f"{name}, skipped: no tokens")
+                    continue
+                self._quantize_one(module, name, entry[0], None, entry[1], None)
+                if on_layer_done is not None:
+                    on_layer_done(name)
+
+        next_q = torch.empty_like(inps_q)
+        forward_input(inps_q, block_q, kwargs, bs, dev, out=next_q)
+        del block_f
+        return next_q, next_f
+
+    def _excluded(self, name):
+        return any(k in name for k in self.cfg.exclude_layer_keywords)
+
+    def _quantize_one(self, module, name, h, c, n, factor):
+        qz = self.quantizer
+        extra = {"factor": factor} if factor is not None else {}
+        if self.dist is not None and isinstance(qz, GPTQ):
+            self.dist.quantize_rows(qz, module, h, c, self.cfg, factor)
+        else:
+            qz.quantize_with_qep(
+                module, quant_input_activation=None, original_input_activation=None,
+                percdamp=self.cfg.percdamp, perccorr=self.cfg.perccorr, hessian=h, delta_hatX=c,
+                nsamples=n if qz.flag_nsamples else None, **extra,
+            )
+        result = qz.results.get(name)
+        if result is None:
+            return
+        w_hat = result.__dict__.get("_device_dequantized")
+        try:
+            if w_hat is None:
+                w_hat = result.compute_dequantized_weight().to(self.device)
+            module.weight.data = w_hat.to(module.weight.dtype).reshape(module.weight.shape)
+        except (ValueError, NotImplementedError):
+            logger.error("Failed to compute dequantized weight for %s. Keeping original weights.", name)
+        result.__dict__.pop("_device_dequantized", None)
+
+
+@torch.no_grad()
+def run_quantize_with_qep_arch(model_config, quantizer: Quantizer, qep_config: QEPConfig,
+                               calibration_config=None, *, report_progress: bool = True,
+                               model=None, model_inputs=None, batch_size: int = 16, dist=None,
+                               activations_on_device: bool = True):
+    """Quantize every target layer of a decoder-only model block by block with QEP
+    (reference :323-627).
+
+    ``model`` / ``model_inputs`` ({"input_ids": LongTensor [N, S], …}) can be given
+    directly; otherwise ``model_config.load_model(device_map="cpu")`` supplies the model
+    and ``calibration_config.model_inputs`` the calibration batch (tokenising a text
+    corpus is not part of this package).  Results land in ``quantizer.results``.
+    """
+    if model is None:
+        model = model_config.load_model(device_map="cpu")
+    if model_inputs is None:
+        model_inputs = getattr(calibration_config, "model_inputs", None)
+        if model_inputs is None:
+            raise ValueError("pass model_inputs (or a calibration_config that carries them)")
+    device = torch.device(qep_config.device or "cuda")
+    if device.type != "cuda":
+        raise RuntimeError("run_quantize_with_qep_arch computes on a CUDA device only")
+
+    quantizer.setup(model)
+    store = device if activations_on_device else torch.device("cpu")
+    # embeddings (and whatever precedes the first block) run where the model lives
+    blocks, inps, kwargs = get_blocks_and_inputs(model, model_inputs, batch_size, store_device=store)
+    inps_q, inps_f = inps, inps.clone()
+    kwargs = move_to_device(kwargs, device)
+
+    block_modules = {m for block in blocks for m in block.modules()}
+    remaining = {n for m, n in quantizer.module_to_name.items() if m in block_modules}
+    total = len(remaining)
+    done = {"k": 0}
+
+    def on_layer_done(label):
+        remaining.discard(label.split(",")[0])
+        done["k"] += 1
+        if report_progress:
+            logger.info("[progress] QEP %d/%d %s", done["k"], total, label)
+
+    runner = BlockQuantizer(quantizer, qep_config, batch_size, device, dist=dist)
+    for idx, block in enumerate(blocks):
+        if not remaining:
+            logger.info("All target layers quantized -- skipping remaining blocks.")
+            break
+        block_q = block.to(device)
+        inps_q, inps_f = runner.run(block_q, inps_q, inps_f, kwargs, on_layer_done)
+        mse = F.mse_loss(inps_q.float(), inps_f.float()).item()
+        logger.info("Block %d MSE: %.6e", idx + 1, mse)
+        block_q.cpu()
+    quantizer.execute_post_processing()

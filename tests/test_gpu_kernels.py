@@ -243,7 +243,8 @@ def test_full_layer_against_reference(K, name):
     assert np.array_equal(out["qzeros"].cpu().numpy(), qz)
     # dequantised weight equals the reference formula applied to our own result
     perm = fac.perm.cpu().numpy().astype(np.int64) if bool(g["actorder"]) else None
-    deq = orc.dequantize_result(qw, out["scales"].cpu(), qz, perm, bits, gs, codes.shape)
+    sc = out["scales"].cpu() if gs != -1 else out["scales"].cpu().reshape(-1, 1)
+    deq = orc.dequantize_result(qw, sc, qz, perm, bits, gs, codes.shape)
     assert np.array_equal(out["dequantized"].cpu().numpy().view(np.uint16), deq.numpy().view(np.uint16))
     # reconstruction error within 0.5 % of the reference's
     w = f16(g["W"])
