@@ -1,0 +1,140 @@
+"""Multi-GPU partitioning of the path: one process per GPU over torch.distributed.
+
+The reference has no multi-GPU quantization path; the path shards naturally in two
+places and this module holds the host logic for both:
+
+* tokens: every rank accumulates H and C over its share of the calibration sequences;
+  ``reduce_moments`` turns the per-rank running means into the global ones with one
+  all-reduce per matrix (weights n_r / N);
+* weight rows: given the (replicated) inverse-Hessian factor, rows of a layer are
+  independent, so each rank corrects and quantizes a slab of rows and the slabs are
+  all-gathered.  Slabs start on multiples of 32 rows so that no packed zero-point word
+  straddles two ranks for any bit width.
+
+The collectives go through torch.distributed (NCCL on GPUs, gloo in the CPU tests).
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def row_slab(out_features: int, rank: int, world: int, align: int = 32):
+    """[first, last) rows of ``rank``: contiguous, aligned, sizes differing by at most
+    one aligned unit; trailing ranks may be empty for small layers."""
+    units = (out_features + align - 1) // align
+    base, extra = divmod(units, world)
+    first_u = rank * base + min(rank, extra)
+    last_u = first_u + base + (1 if rank < extra else 0)
+    return min(first_u * align, out_features), min(last_u * align, out_features)
+
+
+def seq_shard(n_seq: int, rank: int, world: int):
+    """[first, last) calibration sequences of ``rank``."""
+    base, extra = divmod(n_seq, world)
+    first = rank * base + min(rank, extra)
+    return first, first + base + (1 if rank < extra else 0)
+
+
+class ShardedContext:
+    """Token- and row-sharding over a process group."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+    # ---- tokens -------------------------------------------------------------------
+    def reduce_moments(self, h: torch.Tensor, c: Optional[torch.Tensor], n: int):
+        """Per-rank means (2/n_r)·Σ_r → global means (2/N)·Σ.  Returns (h, c, N)."""
+        total = torch.tensor([float(n)], dtype=torch.float64, device=h.device)
+        dist.all_reduce(total, group=self.group)
+        big_n = int(total.item())
+        w = (n / big_n) if big_n > 0 else 0.0
+        h.mul_(w)
+        dist.all_reduce(h, group=self.group)
+        if c is not None:
+            c.mul_(w)
+            dist.all_reduce(c, group=self.group)
+        return h, c, big_n
+
+    # ---- rows ---------------------------------------------------------------------
+    def gather_rows(self, local: torch.Tensor, out_features: int, dim: int, per_row: float = 1.0,
+                    align: int = 32) -> torch.Tensor:
+        """Concatenate every rank's slab along ``dim``.  ``per_row`` is the number of
+        entries along ``dim`` per weight row (bits/32 for packed zero points)."""
+        sizes = []
+        for r in range(self.world):
+            a, b = row_slab(out_features, r, self.world, align)
+            sizes.append(int(round((b - a) * per_row)))
+        biggest = max(sizes)
+        if biggest == 0:
+            return local
+        shape = list(local.shape)
+        shape[dim] = biggest
+        padded = torch.zeros(shape, dtype=local.dtype, device=local.device)
+        padded.narrow(dim, 0, local.shape[dim]).copy_(local)
+        parts = [torch.empty_like(padded) for _ in range(self.world)]
+        dist.all_gather(parts, padded.contiguous(), group=self.group)
+        return torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
+
+    def quantize_rows(self, quantizer, module, h, c, cfg, factor,
+                      compute: Optional[Callable] = None):
+        """Correct and quantize this rank's row slab of ``module`` and assemble the full
+        GPTQResult on every rank (``quantizer.results[name]``).
+
+        ``compute(weight_slab, c) -> dict`` produces the slab's outputs (qweight
+        [in·bits/32, rows], qzeros [G, rows·bits/32], scales [G, rows], zeros [G, rows],
+        dequantized [rows, in]); the default runs the CUDA kernels."""
+        import time
+
+        from . import kernels
+        from .quantizer.gptq._gptq import GPTQ, GPTQResult
+
+        name = quantizer.module_to_name[module]
+        t0 = time.time()
+        bits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
+        gs = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
+        weight = module.weight.data
+        out_features, d = weight.shape
+        first, last = row_slab(out_features, self.rank, self.world)
+        slab = weight[first:last]
+
+        if compute is None:
+            def compute(w_slab, cross):
+                if w_slab.shape[0] == 0:
+                    groups = 1 if gs == -1 else (d + gs - 1) // gs
+                    dev = w_slab.device
+                    return {
+                        "qweight": torch.empty((d * bits // 32, 0), dtype=torch.int32, device=dev),
+                        "qzeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
+                        "scales": torch.empty((groups, 0), dtype=torch.float16, device=dev),
+                        "zeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
+                        "dequantized": torch.empty((0, d), dtype=torch.float16, device=dev),
+                    }
+                if cross is not None:
+                    kernels.qep_adjust(w_slab, cross, factor, cfg.perccorr)
+                return kernels.gptq_quantize(w_slab, factor, wbits=bits, groupsize=gs, sym=quantizer.sym,
+                                             blocksize=quantizer.blocksize, pack=True)
+
+        local = compute(slab, c)
+        qweight = self.gather_rows(local["qweight"], out_features, dim=1)
+        qzeros = self.gather_rows(local["qzeros"], out_features, dim=1, per_row=bits / 32.0)
+        scales = self.gather_rows(local["scales"], out_features, dim=1)
+        w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
+        perm = getattr(factor, "perm", None) if quantizer.actorder else None
+        result = GPTQResult(
+            wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
+            qweight=qweight.cpu(), scales=(scales.cpu() if gs != -1 else scales.cpu().reshape(out_features, 1)),
+            qzeros=qzeros.cpu(), perm=perm.to(torch.int64).cpu() if perm is not None else None,
+            qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(out_features, d),
+        )
+        result.__dict__["_device_dequantized"] = w_hat
+        if weight.is_cuda:
+            torch.cuda.synchronize(weight.device)
+        result.quantization_time = time.time() - t0
+        quantizer.results[name] = result
+        return result
