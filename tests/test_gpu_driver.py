@@ -156,6 +156,7 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act):
     # propagated activations differ from the full-precision ones, but not wildly
     rel = ((inps_q.float() - inps_f.float()).norm() / inps_f.float().norm()).item()
     assert 0 < rel < 0.5
+    matched = total = 0
     for name, (h, c, w_before) in q.inputs.items():
         r = q.results[name]
         i = int(name.split(".")[2])
@@ -169,11 +170,16 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act):
         ref = orc.gptq_quantize(w_adj, h.clone(), wbits=bits, groupsize=gs, sym=sym, actorder=act)
         if act and not np.array_equal(ref["perm"].numpy(), r.perm.numpy()):
             continue   # a near-tie in diag(H) ordered differently: codes are not comparable
-        same = (_codes(r) == ref["qweight"].numpy()).mean()
-        assert same >= 0.999, f"{name}: {same:.5f}"
+        eq = _codes(r) == ref["qweight"].numpy()
+        matched += int(eq.sum())
+        total += eq.size
+        # one row that takes another branch early costs a 256-column layer 0.4 % by itself,
+        # so a single tiny layer gets a looser bound and the bar applies to all layers together
+        assert eq.mean() >= 0.99, f"{name}: {eq.mean():.5f}"
         # the block now holds the dequantised weight
         mod = dict(stack.blocks[i].named_modules())[name.split(".", 3)[3]]
         assert torch.equal(mod.weight.data.cpu(), r.compute_dequantized_weight())
+    assert total > 0 and matched / total >= 0.999, f"{matched / total:.5f} identical codes over all layers"
 
 
 def test_full_driver_on_tiny_llama():

@@ -1,0 +1,98 @@
+"""The multi-rank host logic on CPU: two gloo ranks shard tokens for the moments and
+weight rows for the quantization; the assembled result must equal the unsharded one
+(rows are independent given the inverse-Hessian factor)."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import gptq_oracle as orc
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_row_slab_partition():
+    from onecompression_b200.sharding import row_slab, seq_shard
+
+    for out in (32, 96, 1024, 4096, 14336, 2880, 100):
+        for world in (1, 2, 3, 4, 8):
+            slabs = [row_slab(out, r, world) for r in range(world)]
+            assert slabs[0][0] == 0 and slabs[-1][1] == out
+            for (a, b), (c, d) in zip(slabs, slabs[1:]):
+                assert b == c and a <= b
+            assert all(a % 32 == 0 for a, b in slabs if b > a)
+    for n in (128, 7, 16):
+        for world in (1, 2, 4, 8):
+            parts = [seq_shard(n, r, world) for r in range(world)]
+            assert parts[0][0] == 0 and parts[-1][1] == n
+            assert all(p[1] == q[0] for p, q in zip(parts, parts[1:]))
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.sharding import ShardedContext, row_slab, seq_shard
+
+    ctx = ShardedContext()
+    g = torch.Generator().manual_seed(1)
+    n_seq, seq, d, out = 6, 32, 64, 96
+    xq = torch.randn(n_seq, seq, d, generator=g).half()
+    xf = (xq.float() * (1 + 0.05 * torch.randn(n_seq, seq, d, generator=g))).half()
+    w = (torch.randn(out, d, generator=g) * 0.02).half()
+
+    # tokens: per-rank running means -> global means
+    a, b = seq_shard(n_seq, rank, world)
+    h_loc, c_loc, n_loc = orc.hessian_and_crossterm([xq[a:b]], [xf[a:b]])
+    h, c, n = ctx.reduce_moments(h_loc.clone(), c_loc.clone(), n_loc)
+    h_all, c_all, n_all = orc.hessian_and_crossterm([xq], [xf])
+    assert n == n_all
+    assert torch.allclose(h, h_all, rtol=1e-5, atol=1e-6) and torch.allclose(c, c_all, rtol=1e-4, atol=1e-6)
+
+    # rows: every rank quantizes its slab with the oracle standing in for the kernels
+    u = orc.inverse_hessian_upper(h_all.clone(), 0.01)
+    lin = torch.nn.Linear(d, out, bias=False).half()
+    lin.weight.data = w.clone()
+    q = GPTQ(wbits=4, groupsize=32, sym=False)
+    q.module_to_name = {lin: "layer"}
+
+    def compute(w_slab, cross):
+        wa = orc.qep_adjust_weight(w_slab, h_all, cross, 0.01, 0.5)
+        r = orc.gptq_quantize(wa, h_all.clone(), wbits=4, groupsize=32, sym=False, u_override=u)
+        qw, qz = orc.pack_result(r["qweight"].numpy(), r["qzeros"].numpy(), 4)
+        deq = orc.dequantize_result(qw, r["scales"], qz, None, 4, 32, wa.shape)
+        return {"qweight": torch.from_numpy(qw), "qzeros": torch.from_numpy(qz), "scales": r["scales"],
+                "zeros": r["qzeros"], "dequantized": deq}
+
+    class F:  # stands in for the device factor
+        perm = None
+
+    res = ctx.quantize_rows(q, lin, h_all, c_all, QEPConfig(), F(), compute=compute)
+    whole = compute(w, c_all)
+    assert np.array_equal(res.qweight.numpy(), whole["qweight"].numpy())
+    assert np.array_equal(res.qzeros.numpy(), whole["qzeros"].numpy())
+    assert torch.equal(res.scales, whole["scales"])
+    assert torch.equal(res.__dict__["_device_dequantized"], whole["dequantized"])
+    assert q.results["layer"] is res
+    open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_token_and_row_sharding_two_ranks(tmp_path, world):
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
