@@ -4,7 +4,7 @@ They stand in for real checkpoints and the C4 calibration set (neither can be
 present offline): random-init decoder blocks with N(0, 0.02²) fp16 weights and
 calibration tokens drawn uniformly from the vocabulary and pushed through a random
 embedding table.  Tests and the benchmark feed the same tensors to this package and
-to the CPU oracle.
+to the CPU checker of the test-suite.
 """
 
 from __future__ import annotations
