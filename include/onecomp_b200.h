@@ -63,6 +63,28 @@ int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long lo
                     long long ld, float* H, float* C, long long ldh, float a_old, float a_new,
                     int chunk_tokens, int sm_count, int force_simt, int* status, void* stream);
 
+/* Same computation as oc_moment_accum for callers that cannot allocate device memory (no
+ * counterpart in the reference, which allocates freely through torch).  A host that runs
+ * inside another runtime's stream capture, inside a memory pool it does not own, or under a
+ * rule that its device footprint must not grow after start-up cannot provide delta_scratch;
+ * here that scratch is a fixed 32 MiB device array inside the library image, held on every
+ * GPU that loads the library until the process exits.  Inputs and outputs are still the
+ * caller's.  Limits and rules:
+ *   - with C != NULL, n_tok * ld must not exceed oc_moment_static_capacity() (16 Mi fp16
+ *     elements); larger calls return OC_ERR_TOO_LARGE: feed the tokens in several calls;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture;
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating routine;
+ *   - all calls share the one array and it keeps the previous call's contents; nothing in it
+ *     has to start at zero (each call overwrites the part it reads), but two calls that
+ *     overlap on the GPU (different streams, no ordering) race on it: order them.
+ * Everything else (tensor-core path conditions, oc_mirror_upper afterwards, status codes)
+ * is as for oc_moment_accum. */
+long long oc_moment_static_capacity(void);
+int oc_moment_accum_static(const void* xq, const void* xf, long long n_tok, int d, long long ld,
+                           float* H, float* C, long long ldh, float a_old, float a_new,
+                           int chunk_tokens, int sm_count, int* status, void* stream);
+
 /* lower triangle <- upper triangle */
 int oc_mirror_upper(float* M, long long ld, int n, void* stream);
 

@@ -20,6 +20,8 @@ SIGNATURES = {
     "oc_launch_count": (_L, []),
     "oc_launch_count_reset": (_L, []),
     "oc_moment_accum": (_I, [_P, _P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _I, _P, _P]),
+    "oc_moment_static_capacity": (_L, []),
+    "oc_moment_accum_static": (_I, [_P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _P, _P]),
     "oc_mirror_upper": (_I, [_P, _L, _I, _P]),
     "oc_hinv_workspace_bytes": (_L, [_I]),
     "oc_hinv_factor": (_I, [_P, _L, _I, _F, _F, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P]),
