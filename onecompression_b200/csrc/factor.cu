@@ -96,63 +96,146 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
   U[(long long)i * ldu + j] = (j >= i) ? X[(long long)(n - 1 - i) * ldx + (n - 1 - j)] : 0.f;
 }
 
-// ---- one diagonal block: Cholesky in shared memory, then its inverse ---------------------
+// ---- one diagonal block: Cholesky and inverse of a (<=128)^2 block on one SM -----------------
 // A block (nb x nb, lower part read) -> L written back over the lower part;
 // L^-1 written to the matching block of X (lower part; upper part zero).
 // A non-positive or non-finite pivot records (global index + 1) in *status (first one wins)
 // and continues with pivot 1 so that every later kernel still terminates.
+//
+// Factorisation: 16 x 16 threads, each holding an 8 x 8 sub-block in registers; per column one
+// thread takes the square root, the 16 threads of that block column scale it and publish it, and
+// every thread below the diagonal applies the rank-1 update to its registers (two barriers per
+// column).  Inverse: block forward substitution, 8 rows at a time; each thread owns one column
+// (two threads share a column and split the inner dimension).
 __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
                                                          float* __restrict__ X, long long ldx,
                                                          int k0, int nb, int* __restrict__ status) {
   extern __shared__ float sm[];
-  float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);
-  float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));
-  const int tid = threadIdx.x;
+  float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
+  float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
+  float* colbuf = sm + 2 * NB * (NB + 1);                                          // [128]
+  float (*P)[8][NB] = reinterpret_cast<float (*)[8][NB]>(colbuf + NB);             // [2][8][128]
+  float (*D)[8] = reinterpret_cast<float (*)[8]>(colbuf + NB + 2 * 8 * NB);        // [8][8]
+  __shared__ float pivot;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int r0 = ty * 8, c0 = tx * 8;
   float* Ab = A + (long long)k0 * lda + k0;
   float* Xb = X + (long long)k0 * ldx + k0;
-  for (int e = tid; e < NB * NB; e += blockDim.x) {
-    const int i = e / NB, j = e % NB;
-    S[i][j] = (i < nb && j <= i) ? Ab[(long long)i * lda + j] : ((i == j) ? 1.f : 0.f);
-  }
-  __syncthreads();
-  for (int j = 0; j < nb; ++j) {
-    if (tid == 0) {
-      float p = S[j][j];
-      if (!(p > 0.f) || !isfinite(p)) {
-        atomicCAS(status, 0, k0 + j + 1);
-        p = 1.f;
+
+  float a[8][8];
+#pragma unroll
+  for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) {
+      const int r = r0 + ii, c = c0 + cc;
+      a[ii][cc] = (r < nb && c <= r) ? Ab[(long long)r * lda + c] : ((r == c) ? 1.f : 0.f);
+    }
+
+  for (int jb = 0; jb < NB / 8; ++jb) {
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int j = jb * 8 + jj;
+      if (ty == jb && tx == jb) {
+        float p = a[jj][jj];
+        if (!(p > 0.f) || !isfinite(p)) {
+          atomicCAS(status, 0, k0 + j + 1);
+          p = 1.f;
+        }
+        p = sqrtf(p);
+        a[jj][jj] = p;
+        pivot = p;
       }
-      S[j][j] = sqrtf(p);
-    }
-    __syncthreads();
-    const float inv = 1.f / S[j][j];
-    for (int i = j + 1 + tid; i < nb; i += blockDim.x) S[i][j] *= inv;
-    __syncthreads();
-    // trailing lower update: S[i][k] -= S[i][j] * S[k][j],  j < k <= i < nb
-    const int m = nb - j - 1;
-    for (int e = tid; e < m * m; e += blockDim.x) {
-      const int i = j + 1 + e / m, k = j + 1 + e % m;
-      if (k <= i) S[i][k] = fmaf(-S[i][j], S[k][j], S[i][k]);
-    }
-    __syncthreads();
-  }
-  // inverse by forward substitution, one column per thread
-  if (tid < NB) {
-    const int c = tid;
-    for (int i = 0; i < NB; ++i) Y[i][c] = 0.f;
-    if (c < nb) {
-      Y[c][c] = 1.f / S[c][c];
-      for (int i = c + 1; i < nb; ++i) {
-        float acc = 0.f;
-        for (int k = c; k < i; ++k) acc = fmaf(S[i][k], Y[k][c], acc);
-        Y[i][c] = -acc / S[i][i];
+      __syncthreads();
+      if (tx == jb && ty >= jb) {
+        const float inv = 1.f / pivot;
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii) {
+          if (r0 + ii > j) {
+            a[ii][jj] *= inv;
+            colbuf[r0 + ii] = a[ii][jj];
+          }
+        }
+      }
+      __syncthreads();
+      if (ty >= tx && tx >= jb) {
+        float rc[8], cv[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { rc[t] = colbuf[r0 + t]; cv[t] = colbuf[c0 + t]; }
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc)
+            if (c0 + cc > j && r0 + ii >= c0 + cc) a[ii][cc] = fmaf(-rc[ii], cv[cc], a[ii][cc]);
       }
     }
   }
+#pragma unroll
+  for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) {
+      const int r = r0 + ii, c = c0 + cc;
+      S[r][c] = (c <= r) ? a[ii][cc] : 0.f;
+      if (r < nb && c <= r) Ab[(long long)r * lda + c] = a[ii][cc];
+    }
   __syncthreads();
+
+  // ---- inverse: rows 8I .. 8I+7 from the rows above ----
+  const int c = tid & (NB - 1), h = tid >> 7;
+  for (int I = 0; I < NB / 8; ++I) {
+    const int i0 = I * 8;
+    if (tid < 8) {
+      // column tid of the inverse of the 8 x 8 diagonal block
+      float x[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        float acc = (r == tid) ? 1.f : 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < r) acc = fmaf(-S[i0 + r][i0 + q], x[q], acc);
+        x[r] = (r >= tid) ? acc / S[i0 + r][i0 + r] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) D[r][tid] = x[r];
+    }
+    float t[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t[r] = 0.f;
+    if (c < i0) {
+      const int half = i0 / 2;
+      int klo = h ? half : 0;
+      const int khi = h ? i0 : half;
+      klo = max(klo, c);      // Y[k][c] = 0 for k < c
+      for (int k = klo; k < khi; ++k) {
+        const float yk = Y[k][c];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t[r] = fmaf(S[i0 + r][k], yk, t[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) P[h][r][c] = t[r];
+    __syncthreads();
+    if (h == 0) {
+      if (c < i0) {
+        float s8[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) s8[r] = P[0][r][c] + P[1][r][c];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          float acc = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            if (q <= r) acc = fmaf(D[r][q], s8[q], acc);
+          Y[i0 + r][c] = -acc;
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) Y[i0 + r][c] = (c < i0 + 8) ? D[r][c - i0] : 0.f;
+      }
+    }
+    __syncthreads();
+  }
   for (int e = tid; e < nb * nb; e += blockDim.x) {
     const int i = e / nb, j = e % nb;
-    if (j <= i) Ab[(long long)i * lda + j] = S[i][j];
     Xb[(long long)i * ldx + j] = (j <= i) ? Y[i][j] : 0.f;
   }
 }
@@ -204,7 +287,7 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
 
   // ---- blocked right-looking Cholesky --------------------------------------------------
   static bool attr_set = false;
-  const int smem = 2 * NB * (NB + 1) * (int)sizeof(float);
+  const int smem = (2 * NB * (NB + 1) + NB + 2 * 8 * NB + 64) * (int)sizeof(float);
   if (!attr_set) {
     OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;

@@ -6,7 +6,7 @@
 // file is compiled with -fmad=false and uses the _rn intrinsics besides).
 //
 // Rows of W are independent given U, so one thread owns one row for a whole
-// block of up to 128 columns: the row's block lives in shared memory, 32
+// block of up to 128 columns: the row's block lives in shared memory, 16
 // columns at a time in registers; the in-block error propagation needs no
 // inter-thread communication at all.  The lazy-batch trailing update
 // W[:, i2:] -= Err * U[i1:i2, i2:] is a launch of the fp32 GEMM engine with
@@ -18,7 +18,7 @@
 namespace {
 
 constexpr int BLK = 128;      // maximum GPTQ block size handled by the column kernel
-constexpr int SUB = 32;       // columns held in registers at a time
+constexpr int SUB = 16;       // columns held in registers at a time
 constexpr int WS = BLK + 4;   // shared tile row stride in floats (odd multiple of 16 bytes)
 
 struct ColArgs {
@@ -45,28 +45,42 @@ __device__ __forceinline__ void params_from_range(float mn, float mx, int maxq, 
   zero = sym ? (float)(maxq + 1) * 0.5f : rintf(__fdiv_rn(-mn, scale));
 }
 
+// WARPS*32 rows per CTA; the CTA always has LOADERS threads so that filling the two shared
+// tiles is not left to a single warp when a CTA owns few rows.
+constexpr int LOADERS = 256;
+
+// Group parameters are fitted on the block-entry values of columns col .. col+gs-1 (the
+// reference, :737-745, reads the matrix, not the block copy).  Kept out of line: it runs once
+// per group and would otherwise be replicated in every unrolled column step.
+__device__ __noinline__ void fit_group(const float* __restrict__ src, int n, int maxq, int sym,
+                                       float* scale, float* zero) {
+  float mn = 0.f, mx = 0.f;
+  for (int t = 0; t < n; ++t) { const float v = src[t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
+  params_from_range(mn, mx, maxq, sym, *scale, *zero);
+}
+
 template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) gptq_block_kernel(ColArgs a) {
+__global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
   extern __shared__ __align__(16) float sm[];
   float* Us = sm;               // [BLK][BLK], upper triangle of the diagonal block of U
   float* Ws = sm + BLK * BLK;   // [WARPS*32][WS], block-entry values of the rows' columns
-  constexpr int NTHR = WARPS * 32;
+  constexpr int NROWS = WARPS * 32;
   const int tid = threadIdx.x;
-  const int row0 = blockIdx.x * NTHR;
+  const int row0 = blockIdx.x * NROWS;
   const int count = a.count, i1 = a.i1;
 
-  for (int e = tid; e < BLK * BLK; e += NTHR) {
+  for (int e = tid; e < BLK * BLK; e += LOADERS) {
     const int i = e / BLK, j = e % BLK;
     Us[e] = (i < count && j < count && j >= i) ? a.U[(long long)(i1 + i) * a.ldu + i1 + j] : 0.f;
   }
-  for (int e = tid; e < NTHR * BLK; e += NTHR) {
+  for (int e = tid; e < NROWS * BLK; e += LOADERS) {
     const int r = e / BLK, c = e % BLK;
     Ws[r * WS + c] = (row0 + r < a.out && c < count) ? a.Wf[(long long)(row0 + r) * a.ldw + i1 + c] : 0.f;
   }
   __syncthreads();
 
   const int row = row0 + tid;
-  if (row >= a.out) return;
+  if (tid >= NROWS || row >= a.out) return;
   float* wrow = Ws + tid * WS;
   const float* grow = a.Wf + (long long)row * a.ldw;  // block-entry state of the whole row
   const float maxqf = (float)a.maxq;
@@ -93,16 +107,9 @@ __global__ void __launch_bounds__(WARPS * 32) gptq_block_kernel(ColArgs a) {
       if (ci < count) {
         const int col = i1 + ci;
         if (gs != -1 && col % gs == 0) {
-          // Group parameters are fitted on the block-entry values of columns
-          // col .. col+gs-1 (reference :737-745 reads the matrix, not the block copy).
           const int n = min(gs, a.d - col);
-          float mn = 0.f, mx = 0.f;
-          if (ci == 0 && n <= count) {
-            for (int t = 0; t < n; ++t) { const float v = wrow[t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
-          } else {
-            for (int t = 0; t < n; ++t) { const float v = grow[col + t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
-          }
-          params_from_range(mn, mx, a.maxq, a.sym, scale, zero);
+          // the shared tile is still pristine only at the very first column of the block
+          fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, &scale, &zero);
           const int g = col / gs;
           a.scales[(long long)g * a.out + row] = scale;
           a.zeros[(long long)g * a.out + row] = zero;
@@ -303,7 +310,7 @@ int launch_block(const ColArgs& a, cudaStream_t stream) {
     OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  gptq_block_kernel<WARPS><<<oc_div_up(a.out, WARPS * 32), WARPS * 32, smem, stream>>>(a);
+  gptq_block_kernel<WARPS><<<oc_div_up(a.out, WARPS * 32), LOADERS, smem, stream>>>(a);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }
