@@ -172,6 +172,13 @@ int oc_dequantize_packed(const int* qweight, const int* qzeros, const void* scal
 int oc_gemm_f32(const float* A, long long lda, const float* B, long long ldb, float* C,
                 long long ldc, int M, int N, int K, float alpha, float beta, int transA,
                 int transB, int flags, void* stream);
+/* Engine behind every fp32 product of this library (oc_gemm_f32, the Cholesky and inverse
+ * updates, the GPTQ trailing update, the QEP products): mode 0 (default) runs 16-byte aligned
+ * operands on the tensor cores as 3xTF32 (fp32-grade accuracy), mode 1 always uses the fp32 FMA
+ * kernel.  Returns the previous mode.  oc_gemm_tc_status() is 0 unless a bounded pipeline wait
+ * of the tensor-core engine expired on the current device (201..205). */
+int oc_set_gemm_engine(int mode);
+int oc_gemm_tc_status(void);
 
 #ifdef __cplusplus
 }

@@ -21,6 +21,7 @@ LIB = os.path.join(HERE, "libonecomp_b200.so")
 SOURCES = {
     "errors.cu": [],
     "gemm.cu": [],
+    "gemm_tc.cu": [],
     "factor.cu": [],
     "gptq.cu": ["-fmad=false"],
     "moment_simt.cu": [],

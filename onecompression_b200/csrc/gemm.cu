@@ -1,4 +1,7 @@
-// fp32 GEMM engine: C = beta*C + alpha*opA(A)*opB(B) with exact fp32 FMA arithmetic.
+// fp32 GEMM engine, FMA version: C = beta*C + alpha*opA(A)*opB(B) with exact fp32 FMA
+// arithmetic.  Products whose operands are 16-byte aligned go to the tensor-core version
+// (gemm_tc.cu, 3xTF32) unless oc_set_gemm_engine(1) pins this one; this kernel takes every
+// other shape and is the reference the tensor-core engine is tested against.
 //
 // One engine serves every fp32 matrix product of the path: the lazy-batch
 // trailing update of the GPTQ column loop, the trailing update and panel solve
@@ -192,9 +195,21 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 }  // namespace
 
+bool oc_gemm_tc_eligible(const OcGemm& g);
+int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream);
+
+static int g_engine_mode = 0;  // 0: tensor cores (3xTF32) when the operands allow it; 1: FMA engine only
+
+extern "C" int oc_set_gemm_engine(int mode) {
+  const int old = g_engine_mode;
+  if (mode == 0 || mode == 1) g_engine_mode = mode;
+  return old;
+}
+
 int oc_gemm_f32_launch(const OcGemm& g, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return OC_OK;
   OC_REQUIRE(g.A && g.B && g.C && g.K >= 0, "gemm: null operand or negative K");
+  if (g_engine_mode == 0 && oc_gemm_tc_eligible(g)) return oc_gemm_tc_launch(g, stream);
   const int tiles_m = oc_div_up(g.M, TM), tiles_n = oc_div_up(g.N, TN);
   OC_REQUIRE(tiles_m <= 65535 && g.batch <= 65535, "gemm: M or batch too large for one launch");
   const bool vec = aligned16(g.A) && aligned16(g.B) && aligned16(g.C) && g.lda % 4 == 0 &&

@@ -1,0 +1,404 @@
+// fp32-accurate GEMM on the tensor cores (3xTF32): C = beta*C + alpha*opA(A)*opB(B).
+//
+// Every fp32 operand value a is split into hi = tf32(a) (round to nearest, low 13 mantissa
+// bits zero) and lo = a - hi (exact in fp32); the product a*b is accumulated as
+// hi*hi + hi*lo + lo*hi with tcgen05.mma.kind::tf32 into an fp32 TMEM accumulator.  The
+// dropped lo*lo term and the truncation of lo to tf32 are about 2^-22 relative, i.e. the
+// result is an fp32-grade product sum.
+//
+// Pipeline of one persistent CTA (128 x 128 output tiles, 32 k-values per stage, 3 stages):
+//   warp 0      TMA: raw fp32 tiles of A and B into shared memory (128-byte swizzle)
+//   warps 2..5  split: rewrite every raw value in place as hi and store lo at the same
+//               offset of a second buffer (elementwise, so the swizzled layout is kept)
+//   warp 1      MMA: per 8 k-values three tcgen05.mma (lo*hi, hi*lo, hi*hi), M=128 N=128 K=8
+//   warps 6..9  drain: accumulators leave TMEM every `chunk_k` k-values and are summed in
+//               registers (the tensor core truncates when it accumulates, so chains are kept
+//               short); at the end of a tile alpha / beta are applied and C is written while
+//               the MMA warp already works on the next tile in the other TMEM buffer.
+// Operands may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major); both are
+// native tcgen05 layouts, so the four transpose combinations need no data movement.
+// All mbarrier waits are bounded (see tc_common.cuh).
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace octc;
+
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int OPER_BYTES = BM * BK * 4;                 // 16 KB: one operand tile (hi or lo)
+constexpr int STAGE_BYTES = 4 * OPER_BYTES;             // A hi, A lo, B hi, B lo
+constexpr int SMEM_DYN = STAGES * STAGE_BYTES + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr int N_SPLIT_THREADS = 128;
+
+struct TcGemmParams {
+  float* C; long long ldc; long long strideC;
+  int M, N, K;
+  float alpha, beta;
+  int flags, batch;
+  int tiles_m, tiles_n;
+  int chunk_stages;
+  int* status;
+};
+
+template <bool A_MN, bool B_MN>
+__host__ __device__ constexpr uint32_t idesc() {
+  // c = f32 (1<<4); a, b = tf32 (2<<7, 2<<10); major bits 15 / 16; N>>3 at 17; M>>4 at 24
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// K-major tile: 128 rows (M or N index) of 128 bytes (32 k-values), SWIZZLE_128B;
+//   groups of 8 rows 1024 bytes apart; the next 8 k-values are 32 bytes further in the row.
+// MN-major tile: four 32-column atoms of [32 k-rows x 128 bytes], 4096 bytes apart.  32-bit
+//   MN-major operands exist only in the "128-byte swizzle, 32-byte atom" layout (TMA mode
+//   SWIZZLE_128B_ATOM_32B): the pattern repeats every 4 k-rows (512 bytes), an MMA of 8
+//   k-values spans two such groups, the next 8 k-values start 1024 bytes further.
+template <bool MN>
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, int k8) {
+  uint64_t d;
+  if (MN) {
+    d = (uint64_t)(((addr + k8 * 1024) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(4096 >> 4) << 16;   // leading offset: next 32-column atom
+    d |= (uint64_t)(512 >> 4) << 32;    // stride offset: next group of 4 k-rows
+    d |= 1ull << 61;                    // 128-byte swizzle with 32-byte atoms (the MN-major tf32 layout)
+  } else {
+    d = (uint64_t)(((addr + k8 * 32) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;             // unused for swizzled K-major layouts
+    d |= (uint64_t)(1024 >> 4) << 32;   // next group of 8 rows
+    d |= 2ull << 61;                    // 128-byte swizzle
+  }
+  d |= 1ull << 46;
+  return d;
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t id,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p; }"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(accumulate) : "memory");
+}
+
+template <bool MN>
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, int mn0, int k0,
+                                             int batch, uint32_t bar) {
+  if (MN) {
+#pragma unroll
+    for (int a = 0; a < BM / 32; ++a) tma_load_3d(dst + a * 4096, map, mn0 + a * 32, k0, batch, bar);
+  } else {
+    tma_load_3d(dst, map, k0, mn0, batch, bar);
+  }
+}
+
+__device__ __forceinline__ bool tile_coords(const TcGemmParams& p, int item, int& z, int& m0, int& n0,
+                                            int& k_lo, int& k_hi) {
+  const int per = p.tiles_m * p.tiles_n;
+  z = item / per;
+  const int r = item - z * per;
+  m0 = (r / p.tiles_n) * BM;
+  n0 = (r % p.tiles_n) * BN;
+  if ((p.flags & OC_GEMM_SKIP_UPPER_TILES) && n0 > m0 + BM - 1) return false;
+  k_lo = 0; k_hi = p.K;
+  if (p.flags & OC_GEMM_KLO_FROM_N) k_lo = max(k_lo, n0);
+  if (p.flags & OC_GEMM_KLO_FROM_M) k_lo = max(k_lo, m0);
+  if (p.flags & OC_GEMM_KHI_FROM_M) k_hi = min(k_hi, m0 + BM);
+  if (p.flags & OC_GEMM_KHI_FROM_N) k_hi = min(k_hi, n0 + BN);
+  k_lo = (k_lo / BK) * BK;
+  return true;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const TcGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_raw[STAGES], bar_split[STAGES], bar_empty[STAGES];
+  __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* stage_ptr = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t stage_base = smem_u32(stage_ptr);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_raw[s]), 1);
+      mbar_init(smem_u32(&bar_split[s]), N_SPLIT_THREADS);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), 4); }
+    abort_flag_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(&tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_items = p.batch * p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 1;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int z, m0, n0, k_lo, k_hi;
+        if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+        for (int k0 = k_lo; k0 < k_hi; k0 += BK) {
+          ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 201);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&bar_raw[stage]);
+          const uint32_t sa = stage_base + stage * STAGE_BYTES;
+          mbar_expect_tx(bar, 2 * OPER_BYTES);
+          load_operand<A_MN>(sa, &map_a, m0, k0, z, bar);
+          load_operand<B_MN>(sa + 2 * OPER_BYTES, &map_b, n0, k0, z, bar);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t ID = idesc<A_MN, B_MN>();
+      uint32_t stage = 0, phase = 0, cc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int z, m0, n0, k_lo, k_hi;
+        if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+        const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
+        const int n_chunks = max(1, (n_stages + p.chunk_stages - 1) / p.chunk_stages);
+        for (int ch = 0; ch < n_chunks && ok; ++ch, ++cc) {
+          const uint32_t buf = cc & 1u;
+          ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((cc >> 1) & 1u) ^ 1u, abort_flag, p.status, 202);
+          if (!ok) break;
+          tc_fence_after();
+          const int s_begin = ch * p.chunk_stages;
+          const int s_end = min(n_stages, s_begin + p.chunk_stages);
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          for (int s = s_begin; s < s_end; ++s) {
+            ok = mbar_wait(smem_u32(&bar_split[stage]), phase, abort_flag, p.status, 203);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_hi = stage_base + stage * STAGE_BYTES;
+            const uint32_t a_lo = a_hi + OPER_BYTES, b_hi = a_hi + 2 * OPER_BYTES, b_lo = a_hi + 3 * OPER_BYTES;
+#pragma unroll
+            for (int k8 = 0; k8 < BK / 8; ++k8) {
+              const uint64_t dah = make_desc<A_MN>(a_hi, k8), dal = make_desc<A_MN>(a_lo, k8);
+              const uint64_t dbh = make_desc<B_MN>(b_hi, k8), dbl = make_desc<B_MN>(b_lo, k8);
+              umma_tf32(tmem_d, dal, dbh, ID, (s > s_begin || k8 > 0) ? 1u : 0u);
+              umma_tf32(tmem_d, dah, dbl, ID, 1u);
+              umma_tf32(tmem_d, dah, dbh, ID, 1u);
+            }
+            umma_commit(smem_u32(&bar_empty[stage]));
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (ok) umma_commit(smem_u32(&bar_acc_full[buf]));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // split warps
+    const int st = tid - 64;  // 0..127
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      int z, m0, n0, k_lo, k_hi;
+      if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+      for (int k0 = k_lo; k0 < k_hi; k0 += BK) {
+        ok = mbar_wait(smem_u32(&bar_raw[stage]), phase, abort_flag, p.status, 204);
+        if (!ok) break;
+        uint8_t* base = stage_ptr + stage * STAGE_BYTES;
+#pragma unroll
+        for (int op = 0; op < 2; ++op) {
+          float4* hi = reinterpret_cast<float4*>(base + op * 2 * OPER_BYTES);
+          float4* lo = reinterpret_cast<float4*>(base + op * 2 * OPER_BYTES + OPER_BYTES);
+#pragma unroll
+          for (int i = 0; i < OPER_BYTES / 16 / N_SPLIT_THREADS; ++i) {
+            const int idx = i * N_SPLIT_THREADS + st;
+            const float4 v = hi[idx];
+            float4 h, l;
+            h.x = __uint_as_float((__float_as_uint(v.x) + 0x1000u) & 0xFFFFE000u); l.x = v.x - h.x;
+            h.y = __uint_as_float((__float_as_uint(v.y) + 0x1000u) & 0xFFFFE000u); l.y = v.y - h.y;
+            h.z = __uint_as_float((__float_as_uint(v.z) + 0x1000u) & 0xFFFFE000u); l.z = v.z - h.z;
+            h.w = __uint_as_float((__float_as_uint(v.w) + 0x1000u) & 0xFFFFE000u); l.w = v.w - h.w;
+            hi[idx] = h;
+            lo[idx] = l;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(smem_u32(&bar_split[stage]));
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // drain warps 6..9: TMEM lane quarter = warp % 4
+    const int quarter = warp & 3;
+    uint32_t cc = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      int z, m0, n0, k_lo, k_hi;
+      if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+      const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
+      const int n_chunks = max(1, (n_stages + p.chunk_stages - 1) / p.chunk_stages);
+      float acc[BN];
+#pragma unroll
+      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int ch = 0; ch < n_chunks; ++ch, ++cc) {
+        const uint32_t buf = cc & 1u;
+        ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (cc >> 1) & 1u, abort_flag, p.status, 205);
+        if (!ok) break;
+        tc_fence_after();
+        if (n_stages > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            float v[32];
+            tmem_ld32(taddr + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+      }
+      if (!ok) break;
+      const int row = m0 + quarter * 32 + lane;
+      if (row < p.M) {
+        float* out = p.C + (long long)z * p.strideC + (long long)row * p.ldc;
+        const float alpha = p.alpha, beta = p.beta;
+#pragma unroll
+        for (int c4 = 0; c4 < BN / 4; ++c4) {
+          const int col = n0 + c4 * 4;
+          if (col + 3 < p.N) {
+            float4 o;
+            o.x = alpha * acc[c4 * 4 + 0]; o.y = alpha * acc[c4 * 4 + 1];
+            o.z = alpha * acc[c4 * 4 + 2]; o.w = alpha * acc[c4 * 4 + 3];
+            if (beta != 0.f) {
+              const float4 old = *reinterpret_cast<const float4*>(out + col);
+              o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y);
+              o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w);
+            }
+            *reinterpret_cast<float4*>(out + col) = o;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j < p.N) {
+                const float old = (beta != 0.f) ? beta * out[col + j] : 0.f;
+                out[col + j] = fmaf(alpha, acc[c4 * 4 + j], old);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// rows x K operand.  K-major storage: [rows, K] row-major (ld); MN-major storage: [K, rows].
+int make_operand_map(CUtensorMap* map, const float* ptr, bool mn_major, int rows, int K, long long ld,
+                     long long stride_batch, int batch) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { oc_set_last_error("gemm: cuTensorMapEncodeTiled is not available"); return OC_ERR_CUDA; }
+  cuuint64_t dims[3], strides[2];
+  cuuint32_t box[3], estr[3] = {1, 1, 1};
+  if (mn_major) { dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K; box[0] = 32; box[1] = BK; }
+  else          { dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; box[0] = BK; box[1] = BM; }
+  dims[2] = (cuuint64_t)batch;
+  box[2] = 1;
+  strides[0] = (cuuint64_t)ld * 4;
+  strides[1] = (cuuint64_t)(batch > 1 ? stride_batch : (long long)dims[1] * ld) * 4;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { oc_set_last_error("gemm: cuTensorMapEncodeTiled failed"); return OC_ERR_CUDA; }
+  return OC_OK;
+}
+
+template <bool A_MN, bool B_MN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, int grid, cudaStream_t s) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    OC_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    attr_set = true;
+  }
+  gemm_tf32x3_kernel<A_MN, B_MN><<<grid, NUM_THREADS, SMEM_DYN, s>>>(ma, mb, p);
+  OC_CHECK_LAUNCH();
+  return OC_OK;
+}
+
+int g_sm_count = 0;
+int* g_status[64] = {};
+
+}  // namespace
+
+// The tensor-core engine takes a product when every operand is 16-byte aligned with leading
+// dimensions and batch strides that are multiples of 4 floats; the caller falls back to the
+// FMA engine otherwise.  `status` is a device int (one per device, owned by the library image)
+// that records an expired pipeline wait.
+static __device__ int g_gemm_status_word;
+
+bool oc_gemm_tc_eligible(const OcGemm& g) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(g.A) && al(g.B) && al(g.C) && g.lda % 4 == 0 && g.ldb % 4 == 0 && g.ldc % 4 == 0 &&
+         g.strideA % 4 == 0 && g.strideB % 4 == 0 && g.strideC % 4 == 0 && g.K >= 1 &&
+         (long long)g.M * g.N >= 64 * 64;
+}
+
+int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
+  int dev = 0;
+  OC_CUDA(cudaGetDevice(&dev));
+  OC_REQUIRE(dev >= 0 && dev < 64, "gemm: device index out of range");
+  if (!g_status[dev]) {
+    void* p = nullptr;
+    OC_CUDA(cudaGetSymbolAddress(&p, g_gemm_status_word));
+    g_status[dev] = (int*)p;
+  }
+  if (g_sm_count == 0) {
+    OC_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  CUtensorMap ma, mb;
+  int rc = make_operand_map(&ma, g.A, g.transA != 0, g.M, g.K, g.lda, g.strideA, g.batch);
+  if (rc) return rc;
+  rc = make_operand_map(&mb, g.B, g.transB == 0, g.N, g.K, g.ldb, g.strideB, g.batch);
+  if (rc) return rc;
+  TcGemmParams p{};
+  p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC; p.M = g.M; p.N = g.N; p.K = g.K;
+  p.alpha = g.alpha; p.beta = g.beta; p.flags = g.flags; p.batch = g.batch;
+  p.tiles_m = oc_div_up(g.M, BM); p.tiles_n = oc_div_up(g.N, BN);
+  p.chunk_stages = 8;  // 256 k-values (96 MMAs) per accumulation chain
+  p.status = g_status[dev];
+  const long long items = (long long)p.batch * p.tiles_m * p.tiles_n;
+  OC_REQUIRE(items < (1ll << 30), "gemm: too many tiles");
+  const int grid = (int)((items < g_sm_count) ? items : g_sm_count);
+  const bool a_mn = g.transA != 0, b_mn = g.transB == 0;
+  if (a_mn) return b_mn ? launch<true, true>(ma, mb, p, grid, stream) : launch<true, false>(ma, mb, p, grid, stream);
+  return b_mn ? launch<false, true>(ma, mb, p, grid, stream) : launch<false, false>(ma, mb, p, grid, stream);
+}
+
+// 0 when no tensor-core GEMM on the current device has recorded an expired wait, else its code.
+extern "C" int oc_gemm_tc_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_status_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}

@@ -421,6 +421,16 @@ def dequantize_packed(qweight, qzeros, scales, g_idx, wbits: int, shape) -> torc
     return w
 
 
+def set_gemm_engine(mode: int) -> int:
+    """0: fp32 products run on the tensor cores as 3xTF32 when their operands are 16-byte
+    aligned (default); 1: always the fp32 FMA kernel.  Returns the previous mode."""
+    return _lib.load().oc_set_gemm_engine(int(mode))
+
+
+def gemm_tc_status() -> int:
+    return _lib.load().oc_gemm_tc_status()
+
+
 def gemm_f32(a, b, c=None, alpha=1.0, beta=0.0, trans_a=False, trans_b=False, flags=0):
     """fp32 GEMM engine, exposed for tests: C = beta·C + alpha·op(A)·op(B)."""
     _require_cuda(a, "a")

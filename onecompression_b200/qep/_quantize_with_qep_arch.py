@@ -141,11 +141,114 @@ def _compute_per_module_hessians(block, modules, inps, kwargs, batch_size, devic
     return out
 
 
+class _ForwardMemo:
+    """Keeps outputs of sub-modules of the quantized block that can no longer change, so that
+    later passes over the same inputs skip them.
+
+    The passes of one block all start from the same inputs and the block's layers are
+    replaced in execution order.  A sub-module that contains no layer still waiting to be
+    quantized, and that runs before the first such layer, therefore produces the same output
+    in every later pass: its output is recorded once (per chunk of sequences, in HBM) and the
+    module is then answered from the record.  Candidates are the block's children and their
+    parameter-holding children (norms, projections, the attention module as a whole).
+    """
+
+    def __init__(self, block, pending, n_seq, device, reserve_bytes=8 << 30):
+        self.pending = set(pending)          # target Linear modules not yet quantized
+        self.n_seq = n_seq
+        self.device = device
+        self.reserve = reserve_bytes
+        self.first = 0                       # first sequence of the chunk being forwarded
+        self.cands = []
+        for child in block.children():
+            self.cands.append(child)
+            for sub in child.children():
+                if any(True for _ in sub.parameters()):
+                    self.cands.append(sub)
+        self.inside = {m: {x for x in m.modules() if isinstance(x, nn.Linear)} for m in self.cands}
+        self.cache = {}                      # module -> stored output (tensor or tuple)
+        self._recording = {}
+        self._is_tuple = {}
+        self._handles = []
+        self._stubbed = []
+        self._chunk = 0
+
+    def mark_done(self, module):
+        self.pending.discard(module)
+
+    def _free_bytes(self):
+        free, _ = torch.cuda.mem_get_info(self.device)
+        return free + torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+
+    def _store(self, module, out):
+        rec = self._recording[module]
+        if rec is False:
+            return
+        items = out if isinstance(out, tuple) else (out,)
+        tensors = [t for t in items if isinstance(t, torch.Tensor)]
+        if any(t.dim() < 2 or t.shape[0] != self._chunk for t in tensors) or not tensors:
+            self._recording[module] = False      # not a per-sequence output: leave it alone
+            return
+        if rec is None:
+            need = sum(self.n_seq * t[0].numel() * t.element_size() for t in tensors)
+            if need + self.reserve > self._free_bytes():
+                self._recording[module] = False
+                return
+            rec = [torch.empty((self.n_seq,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+                   if isinstance(t, torch.Tensor) else t for t in items]
+            self._recording[module] = rec
+            self._is_tuple[module] = isinstance(out, tuple)
+        for buf, t in zip(rec, items):
+            if isinstance(t, torch.Tensor):
+                buf[self.first : self.first + t.shape[0]].copy_(t)
+
+    def begin_pass(self, record=True):
+        for m in self.cands:
+            if m in self.cache:
+                bufs, is_tuple = self.cache[m]
+
+                def stub(*_a, _bufs=bufs, _tuple=is_tuple, **_k):
+                    outs = [b[self.first : self.first + self._chunk] if isinstance(b, torch.Tensor) else b
+                            for b in _bufs]
+                    return tuple(outs) if _tuple else outs[0]
+
+                m.forward = stub
+                self._stubbed.append(m)
+            elif record and not (self.inside[m] & self.pending):
+                self._recording[m] = None
+                self._handles.append(m.register_forward_hook(
+                    lambda mod, _inp, out: self._store(mod, out)))
+
+    def set_chunk(self, first, size):
+        self.first, self._chunk = first, size
+
+    def end_pass(self, complete=True):
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+        for m in self._stubbed:
+            del m.forward                    # back to the class's forward
+        self._stubbed = []
+        for m, rec in self._recording.items():
+            if complete and rec not in (None, False):
+                self.cache[m] = (rec, self._is_tuple.get(m, False))
+        self._recording = {}
+        # a cached parent answers for its children: drop their records
+        for m in list(self.cache):
+            for other in self.cands:
+                if other is not m and other in self.cache and other in set(m.modules()):
+                    del self.cache[other]
+
+    def release(self):
+        self.cache = {}
+
+
 class BlockQuantizer:
     """Quantizes the layers of one decoder block with error propagation."""
 
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
-                 dist=None, cache_budget_bytes: Optional[int] = None):
+                 dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True):
+        self.memoize = memoize
         self.quantizer = quantizer
         self.cfg = qep_config
         self.batch_size = batch_size
@@ -220,9 +323,16 @@ class BlockQuantizer:
             for h in handles:
                 h.remove()
 
+        memo = None
+        if self.memoize and torch.device(inps_q.device).type == "cuda":
+            pending = [m for g in regular for m in g if m in qz.module_to_name] + list(experts)
+            memo = _ForwardMemo(block_q, pending, n_seq, dev)
+
         for gi, group in enumerate(regular):
             d = group[0].in_features
             acc = kernels.MomentAccumulator(d, dev, cross=need_c[gi])
+            if memo is not None:
+                memo.begin_pass(record=True)
             cur = {}
             hq = group[0].register_forward_pre_hook(_stop_hook(lambda x: cur.__setitem__("q", x)))
             hf = None
@@ -231,6 +341,8 @@ class BlockQuantizer:
                     _stop_hook(lambda x: cur.__setitem__("f", x)))
             try:
                 for first in range(0, n_seq, bs):
+                    if memo is not None:
+                        memo.set_chunk(first, min(bs, n_seq - first))
                     try:
                         call_block(block_q, inps_q[first : first + bs].to(dev), kwargs)
                     except StopForward:
@@ -250,6 +362,8 @@ class BlockQuantizer:
                 hq.remove()
                 if hf is not None:
                     hf.remove()
+                if memo is not None:
+                    memo.end_pass(complete=True)
             caches[gi] = None
             h, c, n = acc.finalize()
             if self.dist is not None:
@@ -263,6 +377,8 @@ class BlockQuantizer:
                     continue
                 excluded = self._excluded(name)
                 self._quantize_one(module, name, h, None if excluded else c, n, factor)
+                if memo is not None:
+                    memo.mark_done(module)
                 if on_layer_done is not None:
                     on_layer_done(f"{name}, no weight correction" if excluded else name)
 
@@ -281,7 +397,20 @@ class BlockQuantizer:
                     on_layer_done(name)
 
         next_q = torch.empty_like(inps_q)
-        forward_input(inps_q, block_q, kwargs, bs, dev, out=next_q)
+        if memo is not None and not experts:
+            memo.begin_pass(record=False)
+            try:
+                for first in range(0, n_seq, bs):
+                    memo.set_chunk(first, min(bs, n_seq - first))
+                    y = call_block(block_q, inps_q[first : first + bs].to(dev), kwargs)
+                    next_q[first : first + bs].copy_(y)
+            finally:
+                memo.end_pass(complete=False)
+                memo.release()
+        else:
+            if memo is not None:
+                memo.release()
+            forward_input(inps_q, block_q, kwargs, bs, dev, out=next_q)
         del block_f
         return next_q, next_f
 

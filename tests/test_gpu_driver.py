@@ -202,3 +202,27 @@ def test_full_driver_on_tiny_llama():
         assert "lm_head" not in name
         assert r.qweight_is_packed and r.quantization_time > 0
         assert torch.isfinite(r.scales.float()).all()
+
+
+def test_forward_memo_changes_nothing():
+    """Answering finished sub-modules from recorded outputs must give bit-identical results."""
+    from onecompression_b200 import GPTQ, QEPConfig, synthetic
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+
+    shape = dict(synthetic.LLAMA3_8B, hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=64, vocab_size=1000)
+    outs = []
+    for memo in (False, True):
+        stack = synthetic.llama_blocks(shape, 1, 64, DEV, seed=5)
+        x0 = synthetic.embedded_tokens(1000, 256, 40, 64, DEV, seed=5) * 30
+        q = GPTQ(wbits=4, groupsize=128, sym=True)
+        for n, m in stack.blocks[0].named_modules():
+            if isinstance(m, torch.nn.Linear):
+                q.module_to_name[m] = f"model.layers.0.{n}"
+        runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV, memoize=memo)
+        nq, nf = runner.run(stack.blocks[0], x0.clone(), x0.clone(), stack.kwargs)
+        outs.append((nq.cpu(), nf.cpu(), {k: (r.qweight, r.scales, r.qzeros) for k, r in q.results.items()}))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for k in outs[0][2]:
+        for a, b in zip(outs[0][2][k], outs[1][2][k]):
+            assert torch.equal(a, b), k

@@ -38,6 +38,42 @@ def test_gemm_matches_torch_fp32(K, ta, tb, m, n, k):
     assert ((got - want).norm() / want.norm()).item() < 2e-6
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(256, 384, 512), (1000, 520, 260), (128, 128, 32), (72, 4096, 128), (640, 200, 1028)])
+def test_gemm_tensor_core_engine(K, ta, tb, m, n, k):
+    """3xTF32 engine (aligned operands) against float64 and against the FMA engine."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn((k, m) if ta else (m, k), generator=g)
+    b = torch.randn((n, k) if tb else (k, n), generator=g)
+    c0 = torch.randn(m, n, generator=g)
+    want = 0.25 * c0.double() + 2.0 * ((a.t() if ta else a).double() @ (b.t() if tb else b).double())
+    ad, bd = a.to(dev()), b.to(dev())
+    assert K.set_gemm_engine(0) in (0, 1)
+    c_tc = K.gemm_f32(ad, bd, c0.clone().to(dev()), alpha=2.0, beta=0.25, trans_a=ta, trans_b=tb).cpu()
+    K.set_gemm_engine(1)
+    try:
+        c_fma = K.gemm_f32(ad, bd, c0.clone().to(dev()), alpha=2.0, beta=0.25, trans_a=ta, trans_b=tb).cpu()
+    finally:
+        K.set_gemm_engine(0)
+    assert K.gemm_tc_status() == 0
+    e_tc = ((c_tc.double() - want).norm() / want.norm()).item()
+    e_fma = ((c_fma.double() - want).norm() / want.norm()).item()
+    assert e_fma < 1e-6
+    assert e_tc < 2e-6, (e_tc, e_fma)
+
+
+def test_gemm_tensor_core_long_k_same_sign(K):
+    """All-positive operands and K = 8192: the chunked drain keeps the truncation bias of the
+    tensor-core accumulator out of the result."""
+    g = torch.Generator().manual_seed(1)
+    a = torch.rand(256, 8192, generator=g) + 0.5
+    b = torch.rand(8192, 256, generator=g) + 0.5
+    want = a.double() @ b.double()
+    got = K.gemm_f32(a.to(dev()), b.to(dev())).cpu().double()
+    rel = ((got - want).abs() / want).max().item()
+    assert rel < 5e-6, rel
+
+
 def test_gemm_triangular_flags(K):
     g = torch.Generator().manual_seed(5)
     n = 384
