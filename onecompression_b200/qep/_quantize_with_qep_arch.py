@@ -247,8 +247,13 @@ class BlockQuantizer:
     """Quantizes the layers of one decoder block with error propagation."""
 
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
-                 dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True):
+                 dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True,
+                 profile: bool = False):
         self.memoize = memoize
+        # with profile=True every phase is bracketed by device synchronisation and its wall
+        # time is added to self.timings (seconds per phase name); off by default
+        self.profile = profile
+        self.timings = {}
         self.quantizer = quantizer
         self.cfg = qep_config
         self.batch_size = batch_size
@@ -256,10 +261,24 @@ class BlockQuantizer:
         self.dist = dist
         self.cache_budget_bytes = cache_budget_bytes
 
+    def _tick(self, name, t0):
+        if not self.profile:
+            return t0
+        import time
+
+        torch.cuda.synchronize(self.device)
+        now = time.perf_counter()
+        if name is not None:
+            self.timings[name] = self.timings.get(name, 0.0) + now - t0
+        return now
+
     def _budget(self):
         if self.cache_budget_bytes is not None:
             return self.cache_budget_bytes
+        # memory the process could still use: free on the device plus what torch's caching
+        # allocator holds but has not handed out
         free, _total = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
         return int(free * 0.5)
 
     @torch.no_grad()
@@ -267,6 +286,7 @@ class BlockQuantizer:
         """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
         target layers end up holding their dequantized weights."""
         qz, dev, bs = self.quantizer, self.device, self.batch_size
+        t0 = self._tick(None, 0.0)
         block_f = copy.deepcopy(block_q)
         groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
         names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
@@ -314,6 +334,7 @@ class BlockQuantizer:
 
                 handles.append(mods_f[names_q[group[0]]].register_forward_pre_hook(make(gi)))
         next_f = torch.empty_like(inps_f)
+        t0 = self._tick("setup", t0)
         try:
             for first in range(0, n_seq, bs):
                 cursor["first"] = first
@@ -323,6 +344,7 @@ class BlockQuantizer:
             for h in handles:
                 h.remove()
 
+        t0 = self._tick("pass_full_precision", t0)
         memo = None
         if self.memoize and torch.device(inps_q.device).type == "cuda":
             pending = [m for g in regular for m in g if m in qz.module_to_name] + list(experts)
@@ -366,11 +388,14 @@ class BlockQuantizer:
                     memo.end_pass(complete=True)
             caches[gi] = None
             h, c, n = acc.finalize()
+            t0 = self._tick(f"pass_quantized+moments[{gi}]", t0)
             if self.dist is not None:
                 h, c, n = self.dist.reduce_moments(h, c, n)
+                t0 = self._tick("allreduce", t0)
             factor = None
             if isinstance(qz, GPTQ):
                 factor = kernels.factor_hessian(h, qz.percdamp, qz.actorder)
+                t0 = self._tick("factor", t0)
             for module in group:
                 name = qz.module_to_name.get(module)
                 if name is None:
@@ -379,6 +404,7 @@ class BlockQuantizer:
                 self._quantize_one(module, name, h, None if excluded else c, n, factor)
                 if memo is not None:
                     memo.mark_done(module)
+                t0 = self._tick("correct+quantize", t0)
                 if on_layer_done is not None:
                     on_layer_done(f"{name}, no weight correction" if excluded else name)
 
@@ -412,6 +438,7 @@ class BlockQuantizer:
                 memo.release()
             forward_input(inps_q, block_q, kwargs, bs, dev, out=next_q)
         del block_f
+        self._tick("pass_propagate", t0)
         return next_q, next_f
 
     def _excluded(self, name):
