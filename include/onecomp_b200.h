@@ -138,6 +138,16 @@ int oc_gptq_quantize(const void* W, long long ldw, int out, int d, const float* 
                      void* w_hat, long long ldwh, void* workspace, long long workspace_bytes,
                      void* stream);
 
+/* ---- round-to-nearest fallback -----------------------------------------------------
+ * Group-wise RTN of W [out, d] fp16 for MoE experts that saw no calibration token
+ * (_rtn_fallback_result, onecomp/qep/_quantize_with_qep_arch.py:290-320; rule of
+ * pseudo_quantize_tensor, onecomp/quantizer/rtn/quantizer.py:64-181: symmetric range
+ * mirrored on both sides, scale clamped to >= 1e-5).  groupsize -1 = whole row; d must be a
+ * multiple of the group size.  Outputs: scales, zeros fp32 [out, G]; codes int32 [out, d];
+ * deq fp16 [out, d] = fp16((code - zero) * scale). */
+int oc_rtn_quantize(const void* W, long long ldw, int out, int d, int wbits, int groupsize, int sym,
+                    float* scales, float* zeros, int* codes, void* deq, void* stream);
+
 /* ---- QEP weight correction ------------------------------------------------------
  * W <- fp16( Wz + perccorr * (Wz C) (P^T U^T U P) ), Wz = W with dead columns zeroed,
  * in place on W [out, d] fp16.  Replaces Quantizer.adjust_weight's SGEMM, potrf and

@@ -29,6 +29,7 @@ SOURCES = {
     "moment_noalloc.cu": [],
     "pack.cu": [],
     "qep.cu": [],
+    "rtn.cu": ["-fmad=false"],
 }
 
 BASE = [

@@ -342,6 +342,33 @@ def qep_adjust(weight: torch.Tensor, c: torch.Tensor, factor: HessianFactor, per
     return weight
 
 
+def rtn_quantize(weight: torch.Tensor, wbits: int, groupsize: int, sym: bool):
+    """Round-to-nearest group quantization (no Hessian).  Returns dict(codes int32 [out,d],
+    scales fp32 [out,G], zeros fp32 [out,G], dequantized fp16 [out,d]) on the device."""
+    _require_cuda(weight, "weight")
+    if weight.dtype != torch.float16 or weight.dim() != 2:
+        raise TypeError("rtn_quantize expects a 2-D fp16 weight")
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    out, d = weight.shape
+    gs = d if groupsize == -1 else groupsize
+    if d % gs != 0:
+        raise ValueError(f"Tensor shape {d} must be divisible by group size {groupsize}")
+    groups = d // gs
+    dev = weight.device
+    res = {
+        "codes": torch.empty((out, d), dtype=torch.int32, device=dev),
+        "scales": torch.empty((out, groups), dtype=torch.float32, device=dev),
+        "zeros": torch.empty((out, groups), dtype=torch.float32, device=dev),
+        "dequantized": torch.empty((out, d), dtype=torch.float16, device=dev),
+    }
+    with torch.cuda.device(dev):
+        call("oc_rtn_quantize", ptr(weight), weight.stride(0), out, d, wbits, groupsize, 1 if sym else 0,
+             ptr(res["scales"]), ptr(res["zeros"]), ptr(res["codes"]), ptr(res["dequantized"]),
+             stream_handle())
+    return res
+
+
 # ---------------------------------------------------------------------------
 # packed layout utilities
 # ---------------------------------------------------------------------------

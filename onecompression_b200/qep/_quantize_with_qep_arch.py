@@ -141,6 +141,31 @@ def _compute_per_module_hessians(block, modules, inps, kwargs, batch_size, devic
     return out
 
 
+def _rtn_fallback_result(module, quantizer, name):
+    """RTN-quantize a module that saw no calibration token, as a GPTQResult so that it goes
+    through the same save path as its calibrated siblings (reference :290-320): unpacked
+    integer codes, fp16 scales / zeros [G, out], no permutation."""
+    from ..quantizer.gptq._gptq import GPTQResult
+
+    wbits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
+    groupsize = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
+    weight = module.weight.data
+    out = kernels.rtn_quantize(weight if weight.dtype == torch.float16 else weight.half(),
+                               wbits, groupsize, quantizer.sym)
+    scales = out["scales"].to(torch.float16).cpu()
+    zeros = out["zeros"].to(torch.float16).cpu()
+    if groupsize != -1:
+        scales, zeros = scales.T, zeros.T
+    result = GPTQResult(
+        dequantized_weight=out["dequantized"].to(weight.dtype).cpu(), wbits=wbits, groupsize=groupsize,
+        actorder=False, sym=quantizer.sym, qweight=out["codes"].cpu(), scales=scales, qzeros=zeros,
+        perm=None,
+    )
+    # The block continues with compute_dequantized_weight() (fp16 scales), as the reference's
+    # driver does (:599-603), not with RTN's own fp32-scale reconstruction.
+    return result
+
+
 class _ForwardMemo:
     """Keeps outputs of sub-modules of the quantized block that can no longer change, so that
     later passes over the same inputs skip them.
@@ -414,9 +439,18 @@ class BlockQuantizer:
                 name = qz.module_to_name[module]
                 entry = per_module[module]
                 if entry is None:
-                    logger.warning("Expert layer %s received no tokens during calibration; skipping", name)
-                    if on_layer_done is not None:
-                        on_layer_done(f"{name}, skipped: no tokens")
+                    if isinstance(qz, GPTQ):
+                        logger.warning(
+                            "Expert layer %s received no tokens during calibration; falling back to "
+                            "RTN so it stays quantized like its sibling experts", name)
+                        qz.results[name] = _rtn_fallback_result(module, qz, name)
+                        self._install_dequantized(module, name)
+                        if on_layer_done is not None:
+                            on_layer_done(name)
+                    else:
+                        logger.warning("Expert layer %s received no tokens during calibration; skipping", name)
+                        if on_layer_done is not None:
+                            on_layer_done(f"{name}, skipped: no tokens")
                     continue
                 self._quantize_one(module, name, entry[0], None, entry[1], None)
                 if on_layer_done is not None:
@@ -455,7 +489,10 @@ class BlockQuantizer:
                 percdamp=self.cfg.percdamp, perccorr=self.cfg.perccorr, hessian=h, delta_hatX=c,
                 nsamples=n if qz.flag_nsamples else None, **extra,
             )
-        result = qz.results.get(name)
+        self._install_dequantized(module, name)
+
+    def _install_dequantized(self, module, name):
+        result = self.quantizer.results.get(name)
         if result is None:
             return
         w_hat = result.__dict__.get("_device_dequantized")

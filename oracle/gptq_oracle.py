@@ -188,6 +188,46 @@ def dequantize_codes(q, scale, zero):
     return scale * (q.float() - zero)
 
 
+def rtn_quantize(weight: torch.Tensor, wbits: int, groupsize: int, sym: bool):
+    """Round-to-nearest group quantization used for experts without calibration tokens.
+
+    Follows ``run_rtn`` / ``pseudo_quantize_tensor`` (onecomp/quantizer/rtn/rtn_impl.py:22-102,
+    onecomp/quantizer/rtn/quantizer.py:64-181, mse off): per group the range contains 0,
+    symmetric mode mirrors it on both sides, all-zero groups get (-1, +1),
+    scale = max((max-min)/q_max, 1e-5), zero = round(-min/scale) or (q_max+1)/2,
+    dequantized = (q - zero) * scale in the weight's dtype.
+    Returns dict(quantized_weight int32 [out,d], scale fp16 [out,G], zero fp16 [out,G],
+    dequantized_weight)."""
+    w = weight.clone().float()
+    shape = w.shape
+    if groupsize > 0:
+        if w.shape[-1] % groupsize != 0:
+            raise ValueError(f"Tensor shape {w.shape[-1]} must be divisible by group size {groupsize}")
+        w = w.reshape(-1, w.shape[-1] // groupsize, groupsize)
+    else:
+        w = w.reshape(-1, 1, w.shape[-1])
+    q_max = 2**wbits - 1
+    zero_t = torch.zeros(1)
+    w_max = torch.maximum(w.amax(dim=-1, keepdim=True), zero_t)
+    w_min = torch.minimum(w.amin(dim=-1, keepdim=True), zero_t)
+    if sym:
+        w_max = torch.maximum(torch.abs(w_min), w_max)
+        w_min = -w_max
+    flat = (w_min == 0) & (w_max == 0)
+    w_min[flat] = -1
+    w_max[flat] = +1
+    scale = ((w_max - w_min) / q_max).clamp(min=1e-5)
+    zero = torch.full_like(scale, (q_max + 1) / 2) if sym else torch.round(-w_min / scale)
+    q = torch.clamp(torch.round(w / scale) + zero, 0, q_max).int()
+    deq = (q.float() - zero) * scale
+    return {
+        "quantized_weight": q.reshape(shape),
+        "scale": scale.squeeze(-1).to(torch.float16),
+        "zero": zero.squeeze(-1).to(torch.float16),
+        "dequantized_weight": deq.reshape(shape).to(weight.dtype),
+    }
+
+
 # --------------------------------------------------------------------------
 # Inverse-Hessian factor
 # --------------------------------------------------------------------------

@@ -222,6 +222,24 @@ def main(ref_root):
         qweight_packed=res.qweight.numpy(), qzeros_packed=res.qzeros.numpy(),
         scales=_np(res.scales), dequantized=_np(res.compute_dequantized_weight()),
     )
+    # ---- RTN fallback for experts without tokens -----------------------------------------
+    from onecomp.quantizer.rtn.rtn_impl import run_rtn
+
+    rtn = {}
+    w, _ = synth_layer(400, 32, 128, 64)
+    w[3] = 0
+    w[4] = w[4].abs()
+    lin = torch.nn.Linear(128, 32, bias=False).half()
+    lin.weight.data = w.clone()
+    rtn["W"] = _np(w)
+    for bits, gs, sym in ((4, 32, False), (4, 32, True), (3, -1, False), (2, 64, True)):
+        r = run_rtn(lin, wbits=bits, groupsize=gs, sym=sym)
+        key = f"b{bits}_g{gs}_s{int(sym)}"
+        rtn[f"codes_{key}"] = r["quantized_weight"].numpy()
+        rtn[f"scale_{key}"] = _np(r["scale"])
+        rtn[f"zero_{key}"] = _np(r["zero"])
+        rtn[f"deq_{key}"] = _np(r["dequantized_weight"])
+    np.savez_compressed(os.path.join(HERE, "rtn.npz"), **rtn)
     print("golden fixtures written to", HERE)
 
 

@@ -226,3 +226,90 @@ def test_forward_memo_changes_nothing():
     for k in outs[0][2]:
         for a, b in zip(outs[0][2][k], outs[1][2][k]):
             assert torch.equal(a, b), k
+
+
+class _TinyMoEBlock(torch.nn.Module):
+    """Hard-routed MoE block: experts are called with their routed tokens only; the last
+    expert never gets a token."""
+
+    def __init__(self, hidden, inter, n_exp):
+        super().__init__()
+        self.attn_proj = torch.nn.Linear(hidden, hidden, bias=False)
+        self.mlp = torch.nn.Module()
+        self.mlp.router = torch.nn.Linear(hidden, n_exp, bias=False)
+        self.mlp.experts = torch.nn.ModuleList()
+        for _ in range(n_exp):
+            e = torch.nn.Module()
+            e.up_proj = torch.nn.Linear(hidden, inter, bias=False)
+            e.down_proj = torch.nn.Linear(inter, hidden, bias=False)
+            self.mlp.experts.append(e)
+        self.n_exp = n_exp
+
+    def forward(self, x, **_kw):
+        h = x + self.attn_proj(x)
+        flat = h.reshape(-1, h.shape[-1])
+        idx = self.mlp.router(flat)[:, : self.n_exp - 1].argmax(-1)
+        out = torch.zeros_like(flat)
+        for e in range(self.n_exp):
+            sel = idx == e
+            if sel.any():
+                ex = self.mlp.experts[e]
+                out[sel] = ex.down_proj(torch.nn.functional.silu(ex.up_proj(flat[sel])))
+        return h + out.view_as(h)
+
+
+def test_moe_experts_get_their_own_hessians_and_rtn_fallback():
+    """Per-expert Hessians from routed tokens only, no weight correction for experts, RTN for
+    the expert without tokens (reference _quantize_with_qep_arch.py:204-272, 546-613)."""
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+
+    class Rec(_Recorder, GPTQ):
+        pass
+
+    torch.manual_seed(0)
+    hidden, inter, n_exp = 64, 128, 4
+    blk = _TinyMoEBlock(hidden, inter, n_exp).half().to(DEV)
+    for p in blk.parameters():
+        p.data.normal_(0, 0.05)
+    x0 = torch.randn(48, 64, hidden, device=DEV).half()
+    q = Rec(wbits=4, groupsize=32, sym=False, exclude_layer_keywords=["router"])
+    q.seen, q.inputs = [], {}
+    for n, m in blk.named_modules():
+        if isinstance(m, torch.nn.Linear) and "router" not in n:
+            q.module_to_name[m] = f"model.layers.0.{n}"
+    pristine = {n: m.weight.data.clone().cpu() for n, m in blk.named_modules() if isinstance(m, torch.nn.Linear)}
+    runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV)
+    nq, nf = runner.run(blk, x0.clone(), x0.clone(), {})
+    assert torch.isfinite(nq.float()).all()
+    names = set(q.results)
+    assert names == {f"model.layers.0.{n}" for n in pristine if "router" not in n}
+    # the regular layer went through QEP with a cross term, experts without
+    assert q.inputs["model.layers.0.attn_proj"][1] is not None
+    for e in range(n_exp - 1):
+        for proj in ("up_proj", "down_proj"):
+            name = f"model.layers.0.mlp.experts.{e}.{proj}"
+            h, c, w_before = q.inputs[name]
+            assert c is None and torch.equal(w_before, pristine[f"mlp.experts.{e}.{proj}"])
+            ref = orc.gptq_quantize(w_before, h.clone(), wbits=4, groupsize=32, sym=False)
+            r = q.results[name]
+            assert r.qweight_is_packed
+            assert (_codes(r) == ref["qweight"].numpy()).mean() >= 0.99
+    # the unrouted expert: RTN, unpacked, and the block holds its dequantised weight
+    for proj in ("up_proj", "down_proj"):
+        name = f"model.layers.0.mlp.experts.{n_exp - 1}.{proj}"
+        assert name not in q.inputs                      # never handed to the GPTQ path
+        r = q.results[name]
+        ref = orc.rtn_quantize(pristine[f"mlp.experts.{n_exp - 1}.{proj}"], 4, 32, False)
+        assert not r.qweight_is_packed and r.perm is None and r.actorder is False
+        assert np.array_equal(r.qweight.numpy(), ref["quantized_weight"].numpy())
+        assert np.array_equal(r.scales.numpy().view(np.uint16), ref["scale"].T.contiguous().numpy().view(np.uint16))
+        mod = dict(blk.named_modules())[f"mlp.experts.{n_exp - 1}.{proj}"]
+        # the block continues with the result's own reconstruction (fp16 scales), which is
+        # within one fp16 ulp of RTN's fp32-scale reconstruction
+        deq = r.compute_dequantized_weight()
+        assert torch.equal(mod.weight.data.cpu(), deq)
+        a = deq.numpy().view(np.uint16).astype(np.int64)
+        b = ref["dequantized_weight"].numpy().view(np.uint16).astype(np.int64)
+        assert np.abs(a - b).max() <= 1
+        assert torch.equal(r.dequantized_weight, ref["dequantized_weight"])

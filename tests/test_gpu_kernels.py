@@ -316,3 +316,18 @@ def test_qep_adjust_matches_reference(K):
         want = g["adjusted"].astype(np.int64)
         assert (got == want).mean() >= 0.995          # fp16 rounding boundaries
         assert np.abs(got - want).max() <= 1          # never more than one fp16 ulp
+
+
+# ---- RTN fallback -------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("bits,gs,sym", [(4, 32, False), (4, 32, True), (3, -1, False), (2, 64, True)])
+def test_rtn_matches_reference_vectors(K, bits, gs, sym):
+    g = load_golden("rtn.npz")
+    key = f"b{bits}_g{gs}_s{int(sym)}"
+    r = K.rtn_quantize(f16(g["W"]).to(dev()), bits, gs, sym)
+    assert np.array_equal(r["codes"].cpu().numpy(), g[f"codes_{key}"])
+    assert np.array_equal(r["scales"].half().cpu().numpy().view(np.uint16), g[f"scale_{key}"])
+    assert np.array_equal(r["zeros"].half().cpu().numpy().view(np.uint16), g[f"zero_{key}"])
+    assert np.array_equal(r["dequantized"].cpu().numpy().view(np.uint16), g[f"deq_{key}"])
+    with pytest.raises(ValueError):
+        K.rtn_quantize(f16(g["W"]).to(dev()), 4, 48, False)

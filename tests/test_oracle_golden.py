@@ -128,3 +128,16 @@ def test_group_index_rule():
     assert np.array_equal(gi, np.argsort(perm) // 4)
     assert np.array_equal(orc.group_index(None, 4, 8), np.arange(8) // 4)
     assert np.array_equal(orc.group_index(None, -1, 8), np.zeros(8))
+
+
+@pytest.mark.parametrize("bits,gs,sym", [(4, 32, False), (4, 32, True), (3, -1, False), (2, 64, True)])
+def test_rtn_matches_reference(bits, gs, sym):
+    g = load_golden("rtn.npz")
+    key = f"b{bits}_g{gs}_s{int(sym)}"
+    r = orc.rtn_quantize(f16(g["W"]), bits, gs, sym)
+    assert np.array_equal(r["quantized_weight"].numpy(), g[f"codes_{key}"])
+    assert np.array_equal(r["scale"].numpy().view(np.uint16), g[f"scale_{key}"])
+    assert np.array_equal(r["zero"].numpy().view(np.uint16), g[f"zero_{key}"])
+    assert np.array_equal(r["dequantized_weight"].numpy().view(np.uint16), g[f"deq_{key}"])
+    with pytest.raises(ValueError):
+        orc.rtn_quantize(f16(g["W"]), 4, 48, False)
