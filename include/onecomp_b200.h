@@ -119,6 +119,8 @@ int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float r
  *
  * perm / invperm / dead may be NULL (no act-order / no dead columns).
  * blocksize 1..128.  groupsize -1 (per channel) or >= 1; G = 1 or ceil(d/groupsize).
+ * mse != 0 adds the reference's shrink search to every parameter fit (:928-950): int(0.8*q_grid)
+ * candidate ranges p = 1 - i/q_grid, error sum |deq - x|^q_norm, first minimum wins.
  * Outputs, each optional (NULL skips it); ld_out is the row count of the whole
  * layer when `out` is a row slab of it (pass pointers already offset to the slab;
  * slabs must start on multiples of 32 rows), else `out`:
@@ -133,7 +135,8 @@ int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float r
 long long oc_gptq_workspace_bytes(int out, int d, int groupsize);
 int oc_gptq_quantize(const void* W, long long ldw, int out, int d, const float* U, long long ldu,
                      const int* perm, const int* invperm, const unsigned char* dead, int wbits,
-                     int groupsize, int sym, int blocksize, int sm_count, int* qweight, int* qzeros,
+                     int groupsize, int sym, int blocksize, int mse, int q_grid, float q_norm,
+                     int sm_count, int* qweight, int* qzeros,
                      void* scales16, float* scales32, int* zeros, long long ld_out, int* codes,
                      void* w_hat, long long ldwh, void* workspace, long long workspace_bytes,
                      void* stream);

@@ -26,8 +26,8 @@ SIGNATURES = {
     "oc_hinv_workspace_bytes": (_L, [_I]),
     "oc_hinv_factor": (_I, [_P, _L, _I, _F, _F, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P]),
     "oc_gptq_workspace_bytes": (_L, [_I, _I, _I]),
-    "oc_gptq_quantize": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P,
-                              _P, _L, _P, _P, _L, _P, _L, _P]),
+    "oc_gptq_quantize": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P,
+                              _P, _P, _P, _L, _P, _P, _L, _P, _L, _P]),
     "oc_rtn_quantize": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "oc_qep_workspace_bytes": (_L, [_I, _I]),
     "oc_qep_adjust": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _F, _P, _L, _P]),

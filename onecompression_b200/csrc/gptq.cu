@@ -20,6 +20,7 @@ namespace {
 constexpr int BLK = 128;      // maximum GPTQ block size handled by the column kernel
 constexpr int SUB = 16;       // columns held in registers at a time
 constexpr int WS = BLK + 4;   // shared tile row stride in floats (odd multiple of 16 bytes)
+constexpr int SUPER = 4;      // blocks per far trailing update (see oc_gptq_quantize)
 
 struct ColArgs {
   const float* Wf; long long ldw;
@@ -29,13 +30,14 @@ struct ColArgs {
   unsigned short* codesT;
   float* scales; float* zeros;  // [G][out] fp32 (G = 1 for per-channel)
   int gs, maxq, sym;
+  int mse_steps; float mse_grid, mse_norm;   // mse_steps = 0: plain min/max fit
 };
 
 // scale / zero over the values v[0..n), reference: GPTQExcecutor.find_params
 // (onecomp/quantizer/gptq/_gptq.py:886-972, perchannel=True, mse=False)
-__device__ __forceinline__ void params_from_range(float mn, float mx, int maxq, int sym,
+__device__ __forceinline__ void params_from_range(float& mn, float& mx, int maxq, int sym,
                                                   float& scale, float& zero) {
-  // mn <= 0 <= mx on entry
+  // mn <= 0 <= mx on entry; on exit they hold the range the parameters were derived from
   if (sym) {
     mx = fmaxf(fabsf(mn), mx);
     if (mn < 0.f) mn = -mx;
@@ -45,19 +47,50 @@ __device__ __forceinline__ void params_from_range(float mn, float mx, int maxq, 
   zero = sym ? (float)(maxq + 1) * 0.5f : rintf(__fdiv_rn(-mn, scale));
 }
 
-// WARPS*32 rows per CTA; the CTA always has LOADERS threads so that filling the two shared
-// tiles is not left to a single warp when a CTA owns few rows.
-constexpr int LOADERS = 256;
+// |scale*(q - zero) - v|^norm for one value under candidate parameters (the error term of the
+// reference's shrink search, :928-950)
+__device__ __forceinline__ float mse_term(float v, float scale, float zero, float maxqf, float norm) {
+  float q = __fadd_rn(rintf(__fdiv_rn(v, scale)), zero);
+  q = fminf(fmaxf(q, 0.f), maxqf);
+  const float dq = __fmul_rn(scale, __fsub_rn(q, zero));
+  return powf(fabsf(__fsub_rn(dq, v)), norm);
+}
+
+// candidate i of the shrink search: range scaled by p = 1 - i/grid
+__device__ __forceinline__ void mse_candidate(int i, float grid, float mn, float mx, int maxq, int sym,
+                                              float zero_sym, float& scale1, float& zero1) {
+  const float p = (float)(1.0 - (double)i / (double)grid);
+  const float mn1 = __fmul_rn(p, mn), mx1 = __fmul_rn(p, mx);
+  scale1 = __fdiv_rn(__fsub_rn(mx1, mn1), (float)maxq);
+  zero1 = sym ? zero_sym : rintf(__fdiv_rn(-mn1, scale1));
+}
 
 // Group parameters are fitted on the block-entry values of columns col .. col+gs-1 (the
 // reference, :737-745, reads the matrix, not the block copy).  Kept out of line: it runs once
 // per group and would otherwise be replicated in every unrolled column step.
 __device__ __noinline__ void fit_group(const float* __restrict__ src, int n, int maxq, int sym,
-                                       float* scale, float* zero) {
+                                       int mse_steps, float grid, float norm, float* scale, float* zero) {
   float mn = 0.f, mx = 0.f;
   for (int t = 0; t < n; ++t) { const float v = src[t]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
-  params_from_range(mn, mx, maxq, sym, *scale, *zero);
+  float s, z;
+  params_from_range(mn, mx, maxq, sym, s, z);
+  if (mse_steps > 0) {
+    float best = __int_as_float(0x7f800000), bs = s, bz = z;
+    for (int i = 0; i < mse_steps; ++i) {
+      float s1, z1;
+      mse_candidate(i, grid, mn, mx, maxq, sym, z, s1, z1);
+      float err = 0.f;
+      for (int t = 0; t < n; ++t) err += mse_term(src[t], s1, z1, (float)maxq, norm);
+      if (err < best) { best = err; bs = s1; bz = z1; }
+    }
+    s = bs; z = bz;
+  }
+  *scale = s; *zero = z;
 }
+
+// WARPS*32 rows per CTA; the CTA always has LOADERS threads so that filling the two shared
+// tiles is not left to a single warp when a CTA owns few rows.
+constexpr int LOADERS = 256;
 
 template <int WARPS>
 __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
@@ -109,7 +142,8 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
         if (gs != -1 && col % gs == 0) {
           const int n = min(gs, a.d - col);
           // the shared tile is still pristine only at the very first column of the block
-          fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, &scale, &zero);
+          fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, a.mse_steps,
+                    a.mse_grid, a.mse_norm, &scale, &zero);
           const int g = col / gs;
           a.scales[(long long)g * a.out + row] = scale;
           a.zeros[(long long)g * a.out + row] = zero;
@@ -160,7 +194,8 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
 __global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_in, int out, int d,
                                     const int* __restrict__ perm, const unsigned char* __restrict__ dead,
                                     float* __restrict__ Wf, long long ldw, int per_channel, int maxq,
-                                    int sym, float* __restrict__ scales, float* __restrict__ zeros) {
+                                    int sym, int mse_steps, float mse_grid, float mse_norm,
+                                    float* __restrict__ scales, float* __restrict__ zeros) {
   const int row = blockIdx.x;
   const __half* src = W + (long long)row * ldw_in;
   float* dst = Wf + (long long)row * ldw;
@@ -172,7 +207,8 @@ __global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_
     dst[j] = (dead && dead[pj]) ? 0.f : v;
   }
   if (!per_channel) return;
-  __shared__ float smn[32], smx[32];
+  __shared__ float smn[32], smx[32], bc[4];
+  const int nwarp = (blockDim.x + 31) / 32;
   for (int o = 16; o > 0; o >>= 1) {
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -180,11 +216,35 @@ __global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_
   if ((threadIdx.x & 31) == 0) { smn[threadIdx.x >> 5] = mn; smx[threadIdx.x >> 5] = mx; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (blockDim.x + 31) / 32; ++w) { mn = fminf(mn, smn[w]); mx = fmaxf(mx, smx[w]); }
+    for (int w = 1; w < nwarp; ++w) { mn = fminf(mn, smn[w]); mx = fmaxf(mx, smx[w]); }
     float s, z;
     params_from_range(mn, mx, maxq, sym, s, z);
-    scales[row] = s;
-    zeros[row] = z;
+    bc[0] = mn; bc[1] = mx; bc[2] = s; bc[3] = z;
+  }
+  __syncthreads();
+  float best_s = bc[2], best_z = bc[3];
+  if (mse_steps > 0) {
+    // shrink search over the whole (original) row, one block-wide error sum per candidate
+    const float rmn = bc[0], rmx = bc[1], zsym = bc[3];
+    float best = __int_as_float(0x7f800000);
+    for (int i = 0; i < mse_steps; ++i) {
+      float s1, z1;
+      mse_candidate(i, mse_grid, rmn, rmx, maxq, sym, zsym, s1, z1);
+      float err = 0.f;
+      for (int j = threadIdx.x; j < d; j += blockDim.x)
+        err += mse_term(__half2float(src[j]), s1, z1, (float)maxq, mse_norm);
+      for (int o = 16; o > 0; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) smn[threadIdx.x >> 5] = err;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < nwarp; ++w) tot += smn[w];
+      if (tot < best) { best = tot; best_s = s1; best_z = z1; }
+    }
+  }
+  if (threadIdx.x == 0) {
+    scales[row] = best_s;
+    zeros[row] = best_z;
   }
 }
 
@@ -323,7 +383,7 @@ extern "C" long long oc_gptq_workspace_bytes(int out, int d, int groupsize) {
   const long long G = (groupsize == -1) ? 1 : (d + groupsize - 1) / groupsize;
   long long b = 0;
   b += (long long)out * round4(d) * 4;       // Wf
-  b += (long long)BLK * round4(out) * 4;     // ErrT
+  b += (long long)SUPER * BLK * round4(out) * 4;  // ErrT
   b += round4((long long)d * out * 2);       // codesT
   b += 2 * G * (long long)out * 4;           // scales, zeros fp32
   return b + 256;
@@ -333,7 +393,8 @@ extern "C" long long oc_gptq_workspace_bytes(int out, int d, int groupsize) {
 extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d, const float* U,
                                 long long ldu, const int* perm, const int* invperm,
                                 const unsigned char* dead, int wbits, int groupsize, int sym,
-                                int blocksize, int sm_count, int* qweight, int* qzeros, void* scales16_,
+                                int blocksize, int mse, int q_grid, float q_norm, int sm_count,
+                                int* qweight, int* qzeros, void* scales16_,
                                 float* scales32, int* zeros_i32, long long ld_out, int* codes,
                                 void* what_, long long ldwh, void* workspace,
                                 long long workspace_bytes, void* stream_) {
@@ -364,22 +425,38 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
   const long long ldw = round4(d), lde = round4(out);
   char* ws = (char*)workspace;
   float* Wf = (float*)ws;                      ws += (long long)out * ldw * 4;
-  float* ErrT = (float*)ws;                    ws += (long long)BLK * lde * 4;
+  float* ErrT = (float*)ws;                    ws += (long long)SUPER * BLK * lde * 4;
   unsigned short* codesT = (unsigned short*)ws; ws += round4((long long)d * out * 2);
   float* scales = (float*)ws;                  ws += (long long)G * out * 4;
   float* zeros = (float*)ws;
   const int maxq = (1 << wbits) - 1;
 
+  OC_REQUIRE(!mse || (q_grid >= 1 && q_norm > 0.f), "gptq_quantize: mse needs q_grid >= 1 and q_norm > 0");
+  const int mse_steps = mse ? (int)(0.8 * q_grid) : 0;   // maxshrink = 0.8 as in the reference
   gptq_prepare_kernel<<<out, 256, 0, stream>>>(W, ldw_in, out, d, perm, dead, Wf, ldw,
-                                               groupsize == -1 ? 1 : 0, maxq, sym, scales, zeros);
+                                               groupsize == -1 ? 1 : 0, maxq, sym, mse_steps,
+                                               (float)q_grid, q_norm, scales, zeros);
   OC_CHECK_LAUNCH();
 
   if (sm_count <= 0) sm_count = 148;
   const int warps_total = oc_div_up(out, 32);
   const int per_sm = oc_div_up(warps_total, sm_count);
+  // The lazy-batch update is done at two distances.  After each block the columns up to the
+  // end of its group of SUPER blocks are updated at once (they are needed next); the columns
+  // beyond are updated once per group with the errors of all its blocks, which cuts the
+  // read-modify-write traffic on the trailing matrix by SUPER.  Every column still receives
+  // the same updates, grouped differently in the fp32 sum.
+  // A group's parameters are fitted on columns that must carry every earlier update, so the
+  // far update may only be postponed when no group reaches across the end of a block group.
+  const bool two_level = (groupsize == -1) || ((SUPER * blocksize) % groupsize == 0);
+  const int super_cols = (two_level ? SUPER : 1) * blocksize;
   for (int i1 = 0; i1 < d; i1 += blocksize) {
     const int count = min(blocksize, d - i1);
-    ColArgs a{Wf, ldw, out, d, i1, count, U, ldu, ErrT, lde, codesT, scales, zeros, groupsize, maxq, sym};
+    const int s0 = (i1 / super_cols) * super_cols;          // first column of the group
+    const int s1 = min(d, s0 + super_cols);                 // one past its last column
+    float* err_rows = ErrT + (long long)(i1 - s0) * lde;
+    ColArgs a{Wf, ldw, out, d, i1, count, U, ldu, err_rows, lde, codesT, scales, zeros, groupsize, maxq, sym,
+              mse_steps, (float)q_grid, q_norm};
     int rc;
     if (per_sm <= 1) rc = launch_block<1>(a, stream);
     else if (per_sm <= 2) rc = launch_block<2>(a, stream);
@@ -387,12 +464,17 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
     else rc = launch_block<8>(a, stream);
     if (rc) return rc;
     const int i2 = i1 + count;
-    if (i2 < d) {
-      OcGemm g{};
-      g.A = ErrT; g.lda = lde; g.transA = 1;
-      g.B = U + (long long)i1 * ldu + i2; g.ldb = ldu; g.transB = 0;
-      g.C = Wf + i2; g.ldc = ldw;
-      g.M = out; g.N = d - i2; g.K = count; g.alpha = -1.f; g.beta = 1.f; g.flags = 0; g.batch = 1;
+    OcGemm g{};
+    g.lda = lde; g.transA = 1; g.ldb = ldu; g.transB = 0; g.ldc = ldw;
+    g.M = out; g.alpha = -1.f; g.beta = 1.f; g.flags = 0; g.batch = 1;
+    if (i2 < s1) {
+      g.A = err_rows; g.K = count;
+      g.B = U + (long long)i1 * ldu + i2; g.C = Wf + i2; g.N = s1 - i2;
+      rc = oc_gemm_f32_launch(g, stream);
+      if (rc) return rc;
+    } else if (i2 < d) {
+      g.A = ErrT; g.K = s1 - s0;
+      g.B = U + (long long)s0 * ldu + s1; g.C = Wf + s1; g.N = d - s1;
       rc = oc_gemm_f32_launch(g, stream);
       if (rc) return rc;
     }

@@ -246,6 +246,9 @@ def gptq_quantize(
     want_scales_f32: bool = False,
     outputs: Optional[dict] = None,
     ld_out: Optional[int] = None,
+    mse: bool = False,
+    q_grid: int = 600,
+    q_norm: float = 2.4,
 ):
     """Run the column loop on ``weight`` [out, d] fp16 (CUDA) with a ready factor.
 
@@ -306,7 +309,8 @@ def gptq_quantize(
             "oc_gptq_quantize", ptr(weight), weight.stride(0), out, d, ptr(factor.u),
             factor.u.stride(0), ptr(factor.perm) if factor.actorder else None,
             ptr(factor.invperm) if factor.actorder else None, ptr(factor.dead), wbits, groupsize,
-            1 if sym else 0, blocksize, sm_count(dev), ptr(outputs.get("qweight")),
+            1 if sym else 0, blocksize, 1 if mse else 0, int(q_grid), float(q_norm), sm_count(dev),
+            ptr(outputs.get("qweight")),
             ptr(outputs.get("qzeros")), ptr(outputs["scales"]), ptr(outputs.get("scales_f32")),
             ptr(outputs["zeros"]), ld, ptr(outputs.get("codes")), ptr(deq),
             deq.stride(0) if deq is not None else d, ptr(ws), ws.numel(), stream_handle(),
@@ -446,6 +450,38 @@ def dequantize_packed(qweight, qzeros, scales, g_idx, wbits: int, shape) -> torc
         call("oc_dequantize_packed", ptr(qweight), ptr(qzeros), ptr(scales), ptr(g_idx), out, d,
              wbits, ptr(w), d, stream_handle())
     return w
+
+
+_staging = {"buf": None}
+
+
+def to_host(tensors):
+    """Copy device tensors to ordinary host tensors through one reusable page-locked staging
+    buffer and a single synchronisation (None entries pass through).  A layer's results are a
+    handful of small tensors: copied one by one into pageable memory each costs a device
+    synchronisation and runs at a fraction of the link speed, and page-locking fresh memory for
+    every result is slower still."""
+    todo = [(i, t) for i, t in enumerate(tensors) if t is not None and t.is_cuda]
+    outs = list(tensors)
+    if not todo:
+        return outs
+    sizes = [(t.numel() * t.element_size() + 255) // 256 * 256 for _, t in todo]
+    total = sum(sizes)
+    buf = _staging["buf"]
+    if buf is None or buf.numel() < total:
+        buf = torch.empty(max(total, 64 << 20), dtype=torch.uint8, pin_memory=True)
+        _staging["buf"] = buf
+    views, off = [], 0
+    for (i, t), sz in zip(todo, sizes):
+        nbytes = t.numel() * t.element_size()
+        v = buf[off : off + nbytes].view(t.dtype).view(t.shape)
+        v.copy_(t.contiguous(), non_blocking=True)
+        views.append(v)
+        off += sz
+    torch.cuda.current_stream().synchronize()
+    for (i, _), v in zip(todo, views):
+        outs[i] = v.clone()
+    return outs
 
 
 def set_gemm_engine(mode: int) -> int:

@@ -123,8 +123,8 @@ def _dequantize_unpacked(codes, scales, zeros, g_idx):
 class GPTQ(Quantizer):
     """GPTQ quantizer (fields and defaults as the reference, _gptq.py:212-229).
 
-    blocksize ≤ 128 and mse=False are what the CUDA column kernel implements; other
-    values raise at ``setup``.  Modules must live on a CUDA device.
+    blocksize ≤ 128 is what the CUDA column kernel implements (larger values raise at
+    ``setup``).  Modules must live on a CUDA device.
     """
 
     flag_calibration: bool = True
@@ -276,18 +276,19 @@ class GPTQ(Quantizer):
         )
         out_features, in_features = dev_out["shape"]
         perm = dev_out["perm"]
-        if self.bitpack_on_quantize:
-            qweight, qzeros = dev_out["qweight"].cpu(), dev_out["qzeros"].cpu()
-        else:
-            qweight, qzeros = dev_out["codes"].cpu(), dev_out["zeros"].cpu()
-            if gs == -1:
-                qzeros = qzeros.reshape(out_features, 1)
-        scales = dev_out["scales"].cpu()
+        packed = self.bitpack_on_quantize
+        qweight, qzeros, scales, perm_host = kernels.to_host([
+            dev_out["qweight"] if packed else dev_out["codes"],
+            dev_out["qzeros"] if packed else dev_out["zeros"],
+            dev_out["scales"], perm,
+        ])
         if gs == -1:
             scales = scales.reshape(out_features, 1)
+            if not packed:
+                qzeros = qzeros.reshape(out_features, 1)
         result = GPTQResult(
             wbits=bits, groupsize=gs, actorder=self.actorder, sym=self.sym, qweight=qweight,
-            scales=scales, qzeros=qzeros, perm=perm.cpu() if perm is not None else None,
+            scales=scales, qzeros=qzeros, perm=perm_host,
             qweight_is_packed=self.bitpack_on_quantize, qzeros_is_packed=self.bitpack_on_quantize,
             qweight_original_shape=(out_features, in_features),
         )
@@ -371,10 +372,6 @@ def _weight_matrix(layer) -> torch.Tensor:
 def _gptq_device(hessian, layer, blocksize, percdamp, wbits, groupsize, actorder, mse, sym, q_grid,
                  q_norm, pack, factor=None):
     """The whole layer on the GPU; returns device tensors."""
-    if mse:
-        raise NotImplementedError(
-            "mse=True (grid search over shrunk ranges) is not implemented by the CUDA column kernel"
-        )
     w = _weight_matrix(layer)
     if not w.is_cuda:
         raise RuntimeError("GPTQ: the layer must live on a CUDA device (this build has no CPU path)")
@@ -386,7 +383,7 @@ def _gptq_device(hessian, layer, blocksize, percdamp, wbits, groupsize, actorder
         factor = kernels.factor_hessian(hessian.to(w.device), percdamp, actorder)
     out = kernels.gptq_quantize(
         w, factor, wbits=wbits, groupsize=groupsize, sym=sym, blocksize=blocksize, pack=pack,
-        want_codes=not pack, want_dequantized=True,
+        want_codes=not pack, want_dequantized=True, mse=bool(mse), q_grid=q_grid, q_norm=q_norm,
     )
     out["shape"] = (w.shape[0], w.shape[1])
     out["perm"] = factor.perm.to(torch.int64) if actorder else None

@@ -126,10 +126,15 @@ class ShardedContext:
         scales = self.gather_rows(local["scales"], out_features, dim=1)
         w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
         perm = getattr(factor, "perm", None) if quantizer.actorder else None
+        if qweight.is_cuda:
+            qweight, scales, qzeros, perm = kernels.to_host(
+                [qweight, scales, qzeros, perm.to(torch.int64) if perm is not None else None])
+        elif perm is not None:
+            perm = perm.to(torch.int64)
         result = GPTQResult(
             wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
-            qweight=qweight.cpu(), scales=(scales.cpu() if gs != -1 else scales.cpu().reshape(out_features, 1)),
-            qzeros=qzeros.cpu(), perm=perm.to(torch.int64).cpu() if perm is not None else None,
+            qweight=qweight, scales=(scales if gs != -1 else scales.reshape(out_features, 1)),
+            qzeros=qzeros, perm=perm,
             qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(out_features, d),
         )
         result.__dict__["_device_dequantized"] = w_hat

@@ -90,6 +90,8 @@ GPTQ_CASES = [
     ("b4_g32_ragged_d160", 32, 160, 640, dict(wbits=4, groupsize=32, sym=False)),
     ("b4_g128_dead", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=False, _dead=(3, 130))),
     ("b4_g128_block64", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=True, blocksize=64)),
+    ("b4_g128_asym_mse", 32, 256, 1024, dict(wbits=4, groupsize=128, sym=False, mse=True)),
+    ("b3_perchannel_sym_mse", 32, 256, 1024, dict(wbits=3, groupsize=-1, sym=True, mse=True)),
 ]
 
 
@@ -182,7 +184,7 @@ def main(ref_root):
         h, n = qz.calculate_hessian(lin, x.unsqueeze(0))
         raw = ref_gptq.run_gptq(
             h.clone(), lin, blocksize=blocksize, percdamp=0.01, wbits=kw["wbits"],
-            groupsize=kw["groupsize"], actorder=kw.get("actorder", False), mse=False,
+            groupsize=kw["groupsize"], actorder=kw.get("actorder", False), mse=kw.get("mse", False),
             sym=kw["sym"],
         )
         u = ref_gptq._compute_inverse_hessian(_prep_h(h.clone(), raw["perm"]), 0.01)
@@ -193,6 +195,7 @@ def main(ref_root):
             W=_np(w), H=h.numpy(), n=np.int64(n), blocksize=np.int64(blocksize),
             wbits=np.int64(kw["wbits"]), groupsize=np.int64(kw["groupsize"]),
             sym=np.int64(kw["sym"]), actorder=np.int64(kw.get("actorder", False)),
+            mse=np.int64(kw.get("mse", False)),
             codes=raw["qweight"].numpy(), scales=_np(raw["scales"]), qzeros=raw["qzeros"].numpy(),
             perm=_np(raw["perm"]), U=u.numpy(),
             qweight_packed=res.qweight.numpy(), qzeros_packed=res.qzeros.numpy(),

@@ -68,8 +68,8 @@ def test_unpacked_result_and_run_gptq_signature():
     assert not r.qweight_is_packed and r.qweight.shape == (32, 256)
     assert np.array_equal(r.compute_dequantized_weight().numpy().view(np.uint16),
                           r.__dict__["_device_dequantized"].cpu().numpy().view(np.uint16))
-    with pytest.raises(NotImplementedError):
-        run_gptq(h, lin, wbits=4, mse=True)
+    raw_mse = run_gptq(h, lin, wbits=4, groupsize=128, mse=True, sym=False, q_grid=100)
+    assert raw_mse["qweight"].shape == (32, 256)
 
 
 def test_forward_hook_path():

@@ -234,6 +234,7 @@ def _run_case(K, g, use_reference_u):
     return K.gptq_quantize(
         w, fac, wbits=bits, groupsize=gs, sym=bool(g["sym"]), blocksize=int(g["blocksize"]),
         pack=True, want_codes=True, want_dequantized=True, want_scales_f32=True,
+        mse=bool(g.get("mse", 0)),
     ), fac
 
 

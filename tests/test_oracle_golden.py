@@ -79,6 +79,7 @@ def test_gptq_matches_reference(name):
     r = orc.gptq_quantize(
         w, torch.from_numpy(g["H"].copy()), blocksize=int(g["blocksize"]), percdamp=0.01,
         wbits=bits, groupsize=gs, actorder=bool(g["actorder"]), sym=bool(g["sym"]),
+        mse=bool(g.get("mse", 0)),
     )
     assert np.array_equal(r["u"].numpy(), g["U"])
     assert np.array_equal(r["qweight"].numpy(), g["codes"])
