@@ -181,14 +181,17 @@ def run_ours(args):
                 if rank == 0:
                     sampler.start()
                 ev0.record()
+            nxt = stack.blocks[i + 1] if i + 1 < len(stack.blocks) else None
             if e2e:
+                # every step starts from host memory: block weights and both activation sets
                 for k, v in blk.state_dict().items():
                     v.copy_(host_blocks[i][k], non_blocking=True)
                     h2d += v.numel() * v.element_size()
                 cur_q = host_q.to(dev, non_blocking=True)
                 cur_f = host_f.to(dev, non_blocking=True)
                 h2d += 2 * host_q.numel() * 2
-            nq, nf = runner.run(blk, cur_q, cur_f, stack.kwargs)
+                nxt = None      # no work is carried across steps in this mode
+            nq, nf = runner.run(blk, cur_q, cur_f, stack.kwargs, next_block=nxt)
             if e2e:
                 host_q.copy_(nq, non_blocking=True)
                 host_f.copy_(nf, non_blocking=True)

@@ -279,6 +279,8 @@ class BlockQuantizer:
         # time is added to self.timings (seconds per phase name); off by default
         self.profile = profile
         self.timings = {}
+        self._side = None
+        self._prefetched = None
         self.quantizer = quantizer
         self.cfg = qep_config
         self.batch_size = batch_size
@@ -306,19 +308,11 @@ class BlockQuantizer:
         free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
         return int(free * 0.5)
 
-    @torch.no_grad()
-    def run(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None):
-        """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
-        target layers end up holding their dequantized weights."""
-        qz, dev, bs = self.quantizer, self.device, self.batch_size
-        t0 = self._tick(None, 0.0)
-        block_f = copy.deepcopy(block_q)
-        groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
-        names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
-        mods_f = {n: m for n, m in block_f.named_modules() if isinstance(m, nn.Linear)}
-
+    def _classify(self, block, groups):
+        """(regular groups, expert modules) among the target layers of ``block``."""
+        qz = self.quantizer
         regular, experts = [], []
-        for group in groups_q:
+        for group in groups:
             targets = [m for m in group if m in qz.module_to_name]
             if not targets:
                 continue
@@ -328,38 +322,48 @@ class BlockQuantizer:
                 regular.append(group)
         # experts the single-sample grouping pass never routed to (reference :436-461)
         known = set(experts)
-        for _n, m in block_q.named_modules():
+        for _n, m in block.named_modules():
             name = qz.module_to_name.get(m) if isinstance(m, nn.Linear) else None
             if name is not None and ".experts." in name and m not in known:
                 experts.append(m)
                 known.add(m)
+        return regular, experts
 
-        # one pass of the full-precision block: next inputs and every group's input
-        n_seq, seq = inps_f.shape[0], inps_f.shape[1]
-        need_c = []
+    @torch.no_grad()
+    def _full_precision_pass(self, block, inps_f, kwargs):
+        """One pass of the still unmodified block over the full-precision inputs: its outputs
+        (the next block's full-precision inputs) and the input of every group that will need a
+        cross term.  Independent of everything the quantized stream does, so it may run ahead
+        on another CUDA stream (see ``prefetch``)."""
+        qz, dev, bs = self.quantizer, self.device, self.batch_size
+        block_f = copy.deepcopy(block)
+        names = {m: n for n, m in block.named_modules() if isinstance(m, nn.Linear)}
+        mods_f = {n: m for n, m in block_f.named_modules() if isinstance(m, nn.Linear)}
+        regular, _experts = self._classify(block, make_grouped_module(block, inps_f, kwargs, dev))
+        heads, need_c = [], {}
         for group in regular:
-            names = [qz.module_to_name[m] for m in group if m in qz.module_to_name]
-            need_c.append(any(not self._excluded(n) for n in names))
-        cache_bytes = sum(n_seq * seq * g[0].in_features * 2 for g, c in zip(regular, need_c) if c)
+            head = names[group[0]]
+            heads.append(head)
+            targets = [qz.module_to_name[m] for m in group if m in qz.module_to_name]
+            need_c[head] = any(not self._excluded(n) for n in targets)
+        n_seq, seq = inps_f.shape[0], inps_f.shape[1]
+        cache_bytes = sum(n_seq * seq * mods_f[h].in_features * 2 for h in heads if need_c[h])
         use_cache = cache_bytes <= self._budget()
-        caches = [None] * len(regular)
-        handles = []
-        cursor = {"first": 0}
+        caches, handles, cursor = {}, [], {"first": 0}
         if use_cache:
-            for gi, (group, c) in enumerate(zip(regular, need_c)):
-                if not c:
+            for head in heads:
+                if not need_c[head]:
                     continue
-                caches[gi] = torch.empty((n_seq, seq, group[0].in_features), dtype=inps_f.dtype, device=dev)
+                caches[head] = torch.empty((n_seq, seq, mods_f[head].in_features), dtype=inps_f.dtype, device=dev)
 
-                def make(gi):
+                def make(head):
                     def pre_hook(_m, args):
                         x = args[0] if isinstance(args, tuple) else args
-                        caches[gi][cursor["first"] : cursor["first"] + x.shape[0]].copy_(x)
+                        caches[head][cursor["first"] : cursor["first"] + x.shape[0]].copy_(x)
                     return pre_hook
 
-                handles.append(mods_f[names_q[group[0]]].register_forward_pre_hook(make(gi)))
+                handles.append(mods_f[head].register_forward_pre_hook(make(head)))
         next_f = torch.empty_like(inps_f)
-        t0 = self._tick("setup", t0)
         try:
             for first in range(0, n_seq, bs):
                 cursor["first"] = first
@@ -368,7 +372,62 @@ class BlockQuantizer:
         finally:
             for h in handles:
                 h.remove()
+        return {"block_f": block_f, "mods_f": mods_f, "need_c": need_c, "caches": caches,
+                "use_cache": use_cache, "next_f": next_f}
 
+    @torch.no_grad()
+    def prefetch(self, block, inps_f, kwargs):
+        """Start the full-precision pass of ``block`` (the block that ``run`` will get next) on a
+        side stream.  It only depends on ``inps_f`` and on the block's untouched weights, so it
+        overlaps with the latency-bound factorisations and column loops of the current block."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self._side.wait_event(ready)
+        inps_f.record_stream(self._side)
+        with torch.cuda.stream(self._side):
+            res = self._full_precision_pass(block, inps_f, kwargs)
+            done = torch.cuda.Event()
+            done.record(self._side)
+        self._prefetched = (block, res, done)
+
+    def _take_prefetched(self, block):
+        if self._prefetched is None or self._prefetched[0] is not block:
+            self._prefetched = None
+            return None
+        _blk, res, done = self._prefetched
+        self._prefetched = None
+        main = torch.cuda.current_stream(self.device)
+        main.wait_event(done)
+        for t in [res["next_f"], *res["caches"].values()]:
+            t.record_stream(main)
+        for p_ in res["block_f"].parameters():
+            p_.data.record_stream(main)
+        return res
+
+    @torch.no_grad()
+    def run(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None, next_block=None):
+        """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
+        target layers end up holding their dequantized weights.  With ``next_block`` (the block
+        the following call will process, already on the device and unmodified) its
+        full-precision pass is started on a side stream as soon as its inputs exist."""
+        qz, dev, bs = self.quantizer, self.device, self.batch_size
+        t0 = self._tick(None, 0.0)
+        fp = self._take_prefetched(block_q)
+        if fp is None:
+            fp = self._full_precision_pass(block_q, inps_f, kwargs)
+        block_f, mods_f, next_f = fp["block_f"], fp["mods_f"], fp["next_f"]
+        use_cache = fp["use_cache"]
+        if next_block is not None and not self.profile:
+            self.prefetch(next_block, next_f, kwargs)
+        groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
+        names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
+        regular, experts = self._classify(block_q, groups_q)
+        n_seq = inps_q.shape[0]
+        need_c = [fp["need_c"][names_q[g[0]]] for g in regular]
+        caches = [fp["caches"].get(names_q[g[0]]) for g in regular]
         t0 = self._tick("pass_full_precision", t0)
         memo = None
         if self.memoize and torch.device(inps_q.device).type == "cuda":
@@ -552,7 +611,10 @@ def run_quantize_with_qep_arch(model_config, quantizer: Quantizer, qep_config: Q
             logger.info("All target layers quantized -- skipping remaining blocks.")
             break
         block_q = block.to(device)
-        inps_q, inps_f = runner.run(block_q, inps_q, inps_f, kwargs, on_layer_done)
+        upcoming = None
+        if idx + 1 < len(blocks) and remaining:
+            upcoming = blocks[idx + 1].to(device)      # its full-precision pass runs ahead
+        inps_q, inps_f = runner.run(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block=upcoming)
         mse = F.mse_loss(inps_q.float(), inps_f.float()).item()
         logger.info("Block %d MSE: %.6e", idx + 1, mse)
         block_q.cpu()

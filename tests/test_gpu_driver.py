@@ -313,3 +313,34 @@ def test_moe_experts_get_their_own_hessians_and_rtn_fallback():
         b = ref["dequantized_weight"].numpy().view(np.uint16).astype(np.int64)
         assert np.abs(a - b).max() <= 1
         assert torch.equal(r.dequantized_weight, ref["dequantized_weight"])
+
+
+def test_prefetched_full_precision_pass_changes_nothing():
+    """Running the next block's full-precision pass ahead on a side stream gives the same
+    results as running it in line."""
+    from onecompression_b200 import GPTQ, QEPConfig, synthetic
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+
+    shape = dict(synthetic.LLAMA3_8B, hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=64, vocab_size=1000)
+    outs = []
+    for ahead in (False, True):
+        stack = synthetic.llama_blocks(shape, 3, 64, DEV, seed=6)
+        x0 = synthetic.embedded_tokens(1000, 256, 40, 64, DEV, seed=6) * 30
+        q = GPTQ(wbits=3, groupsize=128, sym=True)
+        for i, blk in enumerate(stack.blocks):
+            for n, m in blk.named_modules():
+                if isinstance(m, torch.nn.Linear):
+                    q.module_to_name[m] = f"model.layers.{i}.{n}"
+        runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV)
+        a, b = x0.clone(), x0.clone()
+        for i, blk in enumerate(stack.blocks):
+            nxt = stack.blocks[i + 1] if (ahead and i + 1 < len(stack.blocks)) else None
+            a, b = runner.run(blk, a, b, stack.kwargs, next_block=nxt)
+        torch.cuda.synchronize()
+        outs.append((a.cpu(), b.cpu(), {k: (r.qweight, r.scales, r.qzeros) for k, r in q.results.items()}))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert set(outs[0][2]) == set(outs[1][2]) and len(outs[0][2]) == 21
+    for k in outs[0][2]:
+        for x, y in zip(outs[0][2][k], outs[1][2][k]):
+            assert torch.equal(x, y), k
