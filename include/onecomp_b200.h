@@ -162,6 +162,15 @@ int oc_qep_adjust(void* W, long long ldw, int out, int d, const float* C, long l
                   const float* U, long long ldu, const int* perm, const unsigned char* dead,
                   float perccorr, void* workspace, long long workspace_bytes, void* stream);
 
+/* ---- block passes of the QEP driver ----------------------------------------------------
+ * y = weight * fp16( float(x) * rsqrt(mean(float(x)^2) + eps) ) for x, y [rows, d] fp16 and
+ * weight [d] fp16: the RMSNorm of Llama / Mistral / Qwen blocks in one kernel.  The reference's
+ * driver runs the model's own module here (seven elementwise torch kernels through fp32
+ * temporaries, inside the block forwards of onecomp/qep/_quantize_with_qep_arch.py:179-180 and
+ * onecomp/utils/blockwise.py:527-533). */
+int oc_rmsnorm_f16(const void* x, long long ldx, const void* weight, float eps, long long rows, int d,
+                   void* y, long long ldy, void* stream);
+
 /* ---- packed-layout utilities (onecomp/quantizer/gptq/gptq_layer.py:36-170) --------
  * pack_int_weights / unpack_int_weights: codes int32 [out, d] <-> qweight int32
  * [d*bits/32, out].  pack_zeros / unpack_zeros: zeros int32 [G, out] <-> qzeros int32

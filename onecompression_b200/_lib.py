@@ -31,6 +31,7 @@ SIGNATURES = {
     "oc_rtn_quantize": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "oc_qep_workspace_bytes": (_L, [_I, _I]),
     "oc_qep_adjust": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _F, _P, _L, _P]),
+    "oc_rmsnorm_f16": (_I, [_P, _L, _P, _F, _L, _I, _P, _L, _P]),
     "oc_pack_qweight": (_I, [_P, _I, _I, _I, _P, _P]),
     "oc_unpack_qweight": (_I, [_P, _I, _I, _I, _P, _P]),
     "oc_pack_qzeros": (_I, [_P, _I, _I, _I, _I, _P, _P]),

@@ -30,6 +30,7 @@ SOURCES = {
     "pack.cu": [],
     "qep.cu": [],
     "rtn.cu": ["-fmad=false"],
+    "rmsnorm.cu": [],
 }
 
 BASE = [

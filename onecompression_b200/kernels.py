@@ -452,6 +452,22 @@ def dequantize_packed(qweight, qzeros, scales, g_idx, wbits: int, shape) -> torc
     return w
 
 
+def rmsnorm_f16(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """weight * fp16(float(x) * rsqrt(mean(float(x)²) + eps)) over the last dimension (fp16)."""
+    _require_cuda(x, "x")
+    d = x.shape[-1]
+    if x.dtype != torch.float16 or weight.dtype != torch.float16:
+        raise TypeError("rmsnorm_f16 expects fp16 input and weight")
+    x2 = x.reshape(-1, d)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    y = torch.empty((x2.shape[0], d), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        call("oc_rmsnorm_f16", ptr(x2), x2.stride(0), ptr(weight), float(eps), x2.shape[0], d, ptr(y), d,
+             stream_handle())
+    return y.view(x.shape)
+
+
 _staging = {"buf": None}
 
 

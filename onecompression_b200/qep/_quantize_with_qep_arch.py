@@ -166,6 +166,60 @@ def _rtn_fallback_result(module, quantizer, name):
     return result
 
 
+_RMSNORM_BODY = (
+    "input_dtype = hidden_states.dtype",
+    "hidden_states = hidden_states.to(torch.float32)",
+    "variance = hidden_states.pow(2).mean(-1, keepdim=True)",
+    "hidden_states = hidden_states * torch.rsqrt(variance + self.variance_epsilon)",
+    "return self.weight * hidden_states.to(input_dtype)",
+)
+_rmsnorm_classes: dict = {}
+
+
+def _is_plain_rmsnorm(module) -> bool:
+    """True for modules whose forward is, line for line, the Llama-style RMSNorm (fp32 statistics,
+    downcast, then weight product) - the only formula the fused kernel reproduces."""
+    cls = type(module)
+    if cls not in _rmsnorm_classes:
+        ok = False
+        try:
+            import inspect
+
+            lines = [ln.strip() for ln in inspect.getsource(cls.forward).splitlines()]
+            body = tuple(ln for ln in lines if ln and not ln.startswith(("def ", "#", '"""')))
+            ok = body == _RMSNORM_BODY
+        except (OSError, TypeError):
+            ok = False
+        _rmsnorm_classes[cls] = ok
+    return (_rmsnorm_classes[cls] and hasattr(module, "variance_epsilon")
+            and getattr(module, "weight", None) is not None and module.weight.dtype == torch.float16)
+
+
+class _FusedNorms:
+    """While active, plain RMSNorm modules of the given blocks run as one CUDA kernel."""
+
+    def __init__(self, blocks, enabled=True):
+        self.mods = []
+        if enabled:
+            for b in blocks:
+                self.mods += [m for m in b.modules() if _is_plain_rmsnorm(m) and "forward" not in m.__dict__]
+
+    def __enter__(self):
+        for m in self.mods:
+            def fused(x, _m=m):
+                if x.is_cuda and x.dtype == torch.float16:
+                    return kernels.rmsnorm_f16(x, _m.weight, _m.variance_epsilon)
+                return type(_m).forward(_m, x)
+
+            m.forward = fused
+        return self
+
+    def __exit__(self, *exc):
+        for m in self.mods:
+            m.__dict__.pop("forward", None)
+        return False
+
+
 class _ForwardMemo:
     """Keeps outputs of sub-modules of the quantized block that can no longer change, so that
     later passes over the same inputs skip them.
@@ -237,8 +291,8 @@ class _ForwardMemo:
                             for b in _bufs]
                     return tuple(outs) if _tuple else outs[0]
 
+                self._stubbed.append((m, m.__dict__.get("forward")))
                 m.forward = stub
-                self._stubbed.append(m)
             elif record and not (self.inside[m] & self.pending):
                 self._recording[m] = None
                 self._handles.append(m.register_forward_hook(
@@ -251,8 +305,11 @@ class _ForwardMemo:
         for h in self._handles:
             h.remove()
         self._handles = []
-        for m in self._stubbed:
-            del m.forward                    # back to the class's forward
+        for m, previous in self._stubbed:
+            if previous is None:
+                del m.forward                # back to the class's forward
+            else:
+                m.forward = previous
         self._stubbed = []
         for m, rec in self._recording.items():
             if complete and rec not in (None, False):
@@ -273,8 +330,11 @@ class BlockQuantizer:
 
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
                  dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True,
-                 profile: bool = False):
+                 profile: bool = False, fuse_rmsnorm: bool = True):
         self.memoize = memoize
+        # Llama-style RMSNorm modules of the block run as one kernel during the passes (same
+        # rounding points as the module; the row sum is formed in another order)
+        self.fuse_rmsnorm = fuse_rmsnorm
         # with profile=True every phase is bracketed by device synchronisation and its wall
         # time is added to self.timings (seconds per phase name); off by default
         self.profile = profile
@@ -365,10 +425,11 @@ class BlockQuantizer:
                 handles.append(mods_f[head].register_forward_pre_hook(make(head)))
         next_f = torch.empty_like(inps_f)
         try:
-            for first in range(0, n_seq, bs):
-                cursor["first"] = first
-                y = call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
-                next_f[first : first + bs].copy_(y)
+            with _FusedNorms([block_f], self.fuse_rmsnorm):
+                for first in range(0, n_seq, bs):
+                    cursor["first"] = first
+                    y = call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
+                    next_f[first : first + bs].copy_(y)
         finally:
             for h in handles:
                 h.remove()
@@ -422,6 +483,12 @@ class BlockQuantizer:
         use_cache = fp["use_cache"]
         if next_block is not None and not self.profile:
             self.prefetch(next_block, next_f, kwargs)
+        with _FusedNorms([block_q, block_f], self.fuse_rmsnorm):
+            return self._run_quantized(block_q, inps_q, inps_f, kwargs, on_layer_done, fp, t0)
+
+    def _run_quantized(self, block_q, inps_q, inps_f, kwargs, on_layer_done, fp, t0):
+        qz, dev, bs = self.quantizer, self.device, self.batch_size
+        block_f, mods_f, next_f, use_cache = fp["block_f"], fp["mods_f"], fp["next_f"], fp["use_cache"]
         groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
         names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
         regular, experts = self._classify(block_q, groups_q)

@@ -332,3 +332,22 @@ def test_rtn_matches_reference_vectors(K, bits, gs, sym):
     assert np.array_equal(r["dequantized"].cpu().numpy().view(np.uint16), g[f"deq_{key}"])
     with pytest.raises(ValueError):
         K.rtn_quantize(f16(g["W"]).to(dev()), 4, 48, False)
+
+
+# ---- fused RMSNorm of the block passes ------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,d", [(64, 4096), (33, 2880), (5, 100)])
+def test_rmsnorm_matches_module_formula(K, rows, d):
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+
+    g = torch.Generator().manual_seed(d)
+    x = (torch.randn(rows, d, generator=g) * 3).half().to(dev())
+    mod = LlamaRMSNorm(d, eps=1e-5).half().to(dev())
+    mod.weight.data = (1 + 0.1 * torch.randn(d, generator=g)).half().to(dev())
+    with torch.no_grad():
+        want = mod(x)
+        got = K.rmsnorm_f16(x, mod.weight.data, mod.variance_epsilon)
+    a = got.cpu().numpy().view(np.uint16).astype(np.int64)
+    b = want.cpu().numpy().view(np.uint16).astype(np.int64)
+    assert np.abs(a - b).max() <= 1                 # same rounding points; the row sum is ordered differently
+    assert (a == b).mean() > 0.999
