@@ -354,6 +354,26 @@ class GPTQ(Quantizer):
         return quant_config
 
 
+def _create_inference_layer(self, result, linear_module, **kwargs):
+    """Build a GPTQLinear from a GPTQResult (reference :568-591)."""
+    from .gptq_layer import GPTQLinear
+
+    pack_weights = kwargs.get("pack_weights", True)
+    if pack_weights and not is_packable_wbits(result.wbits):
+        raise ValueError(
+            f"pack_weights=True supports only GPTQ wbits in {tuple(sorted(PACKABLE_WBITS))}; "
+            f"got {result.wbits}. Use pack_weights=False for unpacked GPTQ results."
+        )
+    bias = getattr(linear_module, "bias", None)
+    return GPTQLinear.from_quantization_result(
+        result=result, bias=bias, device=linear_module.weight.device, pack_weights=pack_weights,
+        use_gemlite=kwargs.get("use_gemlite"),
+    )
+
+
+GPTQ.create_inference_layer = _create_inference_layer
+
+
 def _weight_matrix(layer) -> torch.Tensor:
     """2-D [out, in] view of the layer's weight (Conv2d flattened, Conv1D transposed)."""
     w = layer.weight.data

@@ -344,3 +344,47 @@ def test_prefetched_full_precision_pass_changes_nothing():
     for k in outs[0][2]:
         for x, y in zip(outs[0][2][k], outs[1][2][k]):
             assert torch.equal(x, y), k
+
+
+@pytest.mark.parametrize("bits,gs,act", [(4, 128, True), (3, 64, False), (8, -1, False)])
+def test_inference_layer_consumes_packed_result(bits, gs, act):
+    """GPTQLinear built from a result reproduces the dequantized weight and maps inputs with it
+    (reference test_gptq.py:287-304: forward vs dequantized weight below 1e-2); its buffers are
+    the safetensors keys of the AutoGPTQ v1 layout."""
+    from onecompression_b200 import GPTQ
+    from onecompression_b200.quantizer.gptq import GPTQLinear
+
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(256, 96, bias=True).half().to(DEV)
+    x = torch.randn(4, 64, 256, device=DEV).half()
+    q = GPTQ(wbits=bits, groupsize=gs, sym=False, actorder=act)
+    q.module_to_name = {lin: "l"}
+    h, _ = q.calculate_hessian(lin, x)
+    r = q.quantize_layer(lin, None, hessian=h)
+    layer = q.create_inference_layer(r, lin)
+    assert isinstance(layer, GPTQLinear)
+    sd = layer.state_dict()
+    groups = 1 if gs == -1 else 256 // gs
+    assert set(sd) == {"qweight", "qzeros", "scales", "g_idx", "bias"}
+    assert sd["qweight"].shape == (256 * bits // 32, 96) and sd["qweight"].dtype == torch.int32
+    assert sd["qzeros"].shape == (groups, 96 * bits // 32) and sd["scales"].shape == (groups, 96)
+    assert sd["g_idx"].dtype == torch.int32 and sd["g_idx"].shape == (256,)
+    assert torch.equal(sd["qweight"].cpu(), r.qweight) and torch.equal(sd["qzeros"].cpu(), r.qzeros)
+    if act:
+        assert torch.equal(sd["g_idx"].cpu().long(), torch.argsort(r.perm) // gs)
+    w_hat = r.compute_dequantized_weight()
+    assert torch.equal(layer.dequantized_weight().cpu(), w_hat)
+    with torch.no_grad():
+        y = layer(x)
+        y_ref = torch.nn.functional.linear(x, w_hat.to(DEV), lin.bias)
+    assert (y - y_ref).abs().max().item() < 1e-2
+    layer.unpack_in_place()
+    assert layer.qweight.shape == (96, 256)
+    assert torch.equal(layer.dequantized_weight().cpu(), w_hat)
+    layer.pack_in_place()
+    assert torch.equal(layer.qweight.cpu(), r.qweight)
+    # apply_results_to_model swaps the module in place
+    model = torch.nn.Sequential(lin)
+    q.results = {"0": r}
+    q.apply_results_to_model(model)
+    assert isinstance(model[0], GPTQLinear)
