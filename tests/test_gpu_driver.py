@@ -388,3 +388,37 @@ def test_inference_layer_consumes_packed_result(bits, gs, act):
     q.results = {"0": r}
     q.apply_results_to_model(model)
     assert isinstance(model[0], GPTQLinear)
+
+
+def test_chunked_calibration_matches_single_pass():
+    """Chunked calibration (no propagation): Hessians accumulated over chunks of sequences equal
+    those of one pass over all sequences, layers that share an input share one accumulation, and
+    two quantizers are served from the same moments (reference chunked_quantization.py:48-171)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200 import GPTQ
+    from onecompression_b200.runner_methods import accumulate_moments, run_chunked_quantization
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2,
+                      num_hidden_layers=2, vocab_size=512, max_position_embeddings=128)
+    model = LlamaForCausalLM(cfg).half().to(DEV).eval()
+    ids = torch.randint(0, 512, (24, 64), device=DEV)
+    q4 = GPTQ(wbits=4, groupsize=128, sym=True)
+    q3 = GPTQ(wbits=3, groupsize=64, sym=False, actorder=True)
+    run_chunked_quantization(None, [q4, q3], None, model=model, model_inputs={"input_ids": ids},
+                             batch_size=8, num_layers_per_group=5, report_progress=False)
+    assert len(q4.results) == len(q3.results) == 14 and q4.module_to_name == {}
+    assert q3.results["model.layers.0.mlp.up_proj"].perm is not None
+    # moments: chunks of 8 against one chunk of 24, and against the forward-hook path
+    q = GPTQ(wbits=4, groupsize=128)
+    q.setup(model)
+    group = list(q.module_to_name.items())[:4]
+    a = accumulate_moments(model, {"input_ids": ids}, group, 8)
+    b = accumulate_moments(model, {"input_ids": ids}, group, 24)
+    mods = [m for m, _ in group]
+    assert a[mods[0]][0].data_ptr() == a[mods[1]][0].data_ptr() == a[mods[2]][0].data_ptr()   # q, k, v share
+    assert a[mods[3]][0].data_ptr() != a[mods[0]][0].data_ptr()
+    for m in mods:
+        assert a[m][1] == b[m][1] == 24 * 64
+        assert ((a[m][0] - b[m][0]).norm() / b[m][0].norm()).item() < 1e-5
