@@ -8,5 +8,6 @@ from . import kernels  # noqa: F401
 from .qep import QEPConfig  # noqa: F401
 from .quantizer import QuantizationResult, Quantizer  # noqa: F401
 from .quantizer.gptq import GPTQ, GPTQResult, run_gptq  # noqa: F401
+from .quantizer.autobit import AutoBitQuantizer  # noqa: F401
 
 __version__ = "0.1.0"

@@ -141,6 +141,16 @@ def _compute_per_module_hessians(block, modules, inps, kwargs, batch_size, devic
     return out
 
 
+def _gptq_of(quantizer, module):
+    """The GPTQ instance that quantizes ``module``: the quantizer itself, the candidate a
+    mixed-precision quantizer assigned to the module, or None for other quantizers."""
+    if isinstance(quantizer, GPTQ):
+        return quantizer
+    child_for = getattr(quantizer, "child_for", None)
+    child = child_for(module) if child_for is not None else None
+    return child if isinstance(child, GPTQ) else None
+
+
 def _rtn_fallback_result(module, quantizer, name):
     """RTN-quantize a module that saw no calibration token, as a GPTQResult so that it goes
     through the same save path as its calibrated siblings (reference :290-320): unpacked
@@ -543,14 +553,19 @@ class BlockQuantizer:
             if self.dist is not None:
                 h, c, n = self.dist.reduce_moments(h, c, n)
                 t0 = self._tick("allreduce", t0)
-            factor = None
-            if isinstance(qz, GPTQ):
-                factor = kernels.factor_hessian(h, qz.percdamp, qz.actorder)
-                t0 = self._tick("factor", t0)
+            factors = {}
             for module in group:
                 name = qz.module_to_name.get(module)
                 if name is None:
                     continue
+                child = _gptq_of(qz, module)
+                factor = None
+                if child is not None:
+                    key = (child.percdamp, child.actorder)
+                    if key not in factors:
+                        factors[key] = kernels.factor_hessian(h, child.percdamp, child.actorder)
+                        t0 = self._tick("factor", t0)
+                    factor = factors[key]
                 excluded = self._excluded(name)
                 self._quantize_one(module, name, h, None if excluded else c, n, factor)
                 if memo is not None:
@@ -565,11 +580,12 @@ class BlockQuantizer:
                 name = qz.module_to_name[module]
                 entry = per_module[module]
                 if entry is None:
-                    if isinstance(qz, GPTQ):
+                    child = _gptq_of(qz, module)
+                    if child is not None:
                         logger.warning(
                             "Expert layer %s received no tokens during calibration; falling back to "
                             "RTN so it stays quantized like its sibling experts", name)
-                        qz.results[name] = _rtn_fallback_result(module, qz, name)
+                        qz.results[name] = _rtn_fallback_result(module, child, name)
                         self._install_dequantized(module, name)
                         if on_layer_done is not None:
                             on_layer_done(name)
@@ -607,8 +623,11 @@ class BlockQuantizer:
     def _quantize_one(self, module, name, h, c, n, factor):
         qz = self.quantizer
         extra = {"factor": factor} if factor is not None else {}
-        if self.dist is not None and isinstance(qz, GPTQ):
-            self.dist.quantize_rows(qz, module, h, c, self.cfg, factor)
+        child = _gptq_of(qz, module)
+        if self.dist is not None and child is not None:
+            self.dist.quantize_rows(child, module, h, c, self.cfg, factor)
+            if child is not qz:
+                qz.results[name] = child.results.pop(name)
         else:
             qz.quantize_with_qep(
                 module, quant_input_activation=None, original_input_activation=None,

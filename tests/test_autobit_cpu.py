@@ -1,0 +1,71 @@
+"""The bit-assignment solver on CPU: optimality against brute force, fused ties, budgets."""
+
+import itertools
+import random
+
+import pytest
+
+from onecompression_b200.quantizer.autobit import effective_bits_per_param, solve_assignment
+
+
+def _brute(errors, params, eff, target, fused):
+    n, nb = len(errors), len(errors[0])
+    budget = target * sum(params)
+    best, arg = float("inf"), None
+    for choice in itertools.product(range(nb), repeat=n):
+        if any(len({choice[m] for m in g}) > 1 for g in fused):
+            continue
+        cost = sum(eff[m][choice[m]] * params[m] for m in range(n))
+        if cost > budget * (1 + 1e-12):
+            continue
+        e = sum(errors[m][choice[m]] for m in range(n))
+        if e < best:
+            best, arg = e, choice
+    return best, arg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_solver_is_optimal_on_small_instances(seed):
+    rnd = random.Random(seed)
+    n, bits = 7, (2, 3, 4)
+    params = [rnd.choice([4096 * 4096, 1024 * 4096, 14336 * 4096]) for _ in range(n)]
+    errors = [sorted((rnd.random() * p / 1e6 for _ in bits), reverse=True) for p in params]
+    eff = [[effective_bits_per_param(b, 128) for b in bits] for _ in range(n)]
+    fused = [[0, 1, 2], [4, 5]]
+    for target in (2.2, 2.9, 3.3, 3.8, 4.2):
+        want, arg = _brute(errors, params, eff, target, fused)
+        chosen, thinned = solve_assignment(errors, params, eff, target, fused)
+        assert not thinned
+        got = sum(errors[m][chosen[m]] for m in range(n))
+        assert abs(got - want) <= 1e-9 * max(1.0, want), (chosen, arg)
+        assert sum(eff[m][chosen[m]] * params[m] for m in range(n)) <= target * sum(params) * (1 + 1e-12)
+        assert chosen[0] == chosen[1] == chosen[2] and chosen[4] == chosen[5]
+
+
+def test_solver_reports_infeasible_budget():
+    with pytest.raises(RuntimeError, match="infeasible"):
+        solve_assignment([[1.0, 0.5]], [100], [[2.1, 4.1]], 1.5)
+
+
+def test_effective_bits_formula():
+    assert effective_bits_per_param(4, 128) == 4 + 20 / 128
+    assert effective_bits_per_param(3, -1, in_features=4096) == 3 + 19 / 4096
+    assert effective_bits_per_param(2, -1) == 2.0
+
+
+def test_model_scale_instance_solves_fast():
+    """280 layers x 3 candidates (the Qwen3-14B size of config 4) stays exact and quick."""
+    import time
+
+    rnd = random.Random(0)
+    shapes = [5120 * 5120, 1024 * 5120, 1024 * 5120, 5120 * 5120, 17408 * 5120, 17408 * 5120, 5120 * 17408]
+    params = shapes * 40
+    errors = [[p * (0.5 + rnd.random()) * s for s in (16.0, 4.0, 1.0)] for p in params]
+    eff = [[effective_bits_per_param(b, 128) for b in (2, 3, 4)] for _ in params]
+    fused = [[7 * l, 7 * l + 1, 7 * l + 2] for l in range(40)] + [[7 * l + 4, 7 * l + 5] for l in range(40)]
+    t = time.time()
+    chosen, thinned = solve_assignment(errors, params, eff, 3.5 + 19.5 / 128, fused)
+    assert time.time() - t < 60
+    used = sum(eff[m][chosen[m]] * params[m] for m in range(len(params))) / sum(params)
+    assert used <= 3.5 + 19.5 / 128 + 1e-9 and used > 3.3
+    assert len(set(chosen)) > 1

@@ -422,3 +422,71 @@ def test_chunked_calibration_matches_single_pass():
     for m in mods:
         assert a[m][1] == b[m][1] == 24 * 64
         assert ((a[m][0] - b[m][0]).norm() / b[m][0].norm()).item() < 1e-5
+
+
+def test_autobit_assignment_and_dispatch_on_tiny_llama():
+    """Mixed-precision assignment: the RTN errors come from the GPU, the chosen candidates are
+    optimal for the oracle's errors, fused layers agree, the budget holds, and every layer is
+    quantized by its assigned candidate through the block driver."""
+    import itertools
+
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import run_quantize_with_qep_arch
+    from onecompression_b200.quantizer.autobit import AutoBitQuantizer, effective_bits_per_param
+
+    torch.manual_seed(1)
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2,
+                      num_hidden_layers=1, vocab_size=512, max_position_embeddings=128)
+    model = LlamaForCausalLM(cfg).half().to(DEV).eval()
+    with torch.no_grad():  # layers of different sensitivity
+        model.model.layers[0].mlp.down_proj.weight.mul_(4.0)
+        model.model.layers[0].self_attn.o_proj.weight.mul_(0.25)
+    cands = [GPTQ(wbits=b, groupsize=32, sym=False) for b in (2, 3, 4)]
+    auto = AutoBitQuantizer(quantizers=cands, target_bit=3.0)
+    auto.setup(model)
+    names = list(auto._name_to_quantizer)
+    assert len(names) == 7
+    chosen = {n: auto._name_to_quantizer[n].wbits for n in names}
+    # oracle errors and brute force over 3^7 assignments
+    mods = dict(model.named_modules())
+    errs, params = {}, {}
+    for n in names:
+        w = mods[n].weight.data.cpu()
+        params[n] = w.numel()
+        errs[n] = []
+        for b in (2, 3, 4):
+            deq = orc.rtn_quantize(w, b, 32, False)["dequantized_weight"].float()
+            errs[n].append(float((w.float() - deq).pow(2).sum()))
+    budget = auto.effective_target_bit * sum(params.values())
+    assert abs(auto.effective_target_bit - effective_bits_per_param(3.0, 32)) < 1e-12
+    best = None
+    for pick in itertools.product(range(3), repeat=7):
+        a = dict(zip(names, pick))
+        qkv = {a[n] for n in names if n.endswith(("q_proj", "k_proj", "v_proj"))}
+        gu = {a[n] for n in names if n.endswith(("gate_proj", "up_proj"))}
+        if len(qkv) > 1 or len(gu) > 1:
+            continue
+        cost = sum(effective_bits_per_param((2, 3, 4)[a[n]], 32) * params[n] for n in names)
+        if cost > budget * (1 + 1e-12):
+            continue
+        e = sum(errs[n][a[n]] for n in names)
+        if best is None or e < best[0]:
+            best = (e, a)
+    assert {n: (2, 3, 4)[i] for n, i in best[1].items()} == chosen
+    assert len(set(chosen.values())) > 1
+    # run the block driver with the assignment
+    auto.module_to_name.clear()
+    for q in cands:
+        q.module_to_name.clear()
+    ids = torch.randint(0, 512, (32, 64), device=DEV)
+    run_quantize_with_qep_arch(None, auto, QEPConfig(device=DEV), None, model=model,
+                               model_inputs={"input_ids": ids}, report_progress=False)
+    assert set(auto.results) == set(names)
+    for n, r in auto.results.items():
+        assert r.wbits == chosen[n] and r.groupsize == 32 and r.qweight_is_packed
+        out, d = r.qweight_original_shape
+        assert r.qweight.shape == (d * r.wbits // 32, out)
+    cfgd = auto.get_quant_config()
+    assert cfgd["quant_method"] == "mixed_gptq" and cfgd["module_wbits"] == chosen
