@@ -281,7 +281,11 @@ def run_ours(args):
         "roofline": {
             "kernel": "moment_tc_kernel (H + C, d=4096, %d tokens per launch)" % ntok,
             "bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["tflops"],
-            "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4), "traffic": None,
+            "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4),
+            # DRAM bytes per launch: the ncu capture of the 16384-token case (1.10 GB read + write,
+            # of which 0.20 GB are the token-independent H and C tiles) scaled to this launch's tokens
+            "traffic": round(0.20e9 + 0.90e9 * ntok / 16384),
+            "traffic_note": "scaled from the ncu capture of a 16384-token launch (profiles/)",
             "peak_source": peaks["src"] + " (burst: kernel timed alone)",
             "flops": "executed MMA flops (upper tiles of H, all of C)",
             "hessian_gemm_tflops_algorithmic": round(algorithmic / (k_ms * 1e-3) / 1e12, 1),
