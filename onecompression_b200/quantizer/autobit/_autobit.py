@@ -290,5 +290,9 @@ class AutoBitQuantizer(Quantizer):
         cfg["module_wbits"] = {n: q.wbits for n, q in self._name_to_quantizer.items()}
         return cfg
 
+    def finalize_quant_config_for_save(self, quant_config, quantized_layer_names, num_hidden_layers=None):
+        return self.quantizers[0].finalize_quant_config_for_save(
+            quant_config, quantized_layer_names, num_hidden_layers=num_hidden_layers)
+
     def create_inference_layer(self, result, linear_module, **kwargs):
         return self.quantizers[0].create_inference_layer(result, linear_module, **kwargs)

@@ -1,0 +1,1 @@
+from .save import build_quantization_config, load_quantized_layers, quantized_state_dict, save_quantized_model  # noqa: F401

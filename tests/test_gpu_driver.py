@@ -490,3 +490,57 @@ def test_autobit_assignment_and_dispatch_on_tiny_llama():
         assert r.qweight.shape == (d * r.wbits // 32, out)
     cfgd = auto.get_quant_config()
     assert cfgd["quant_method"] == "mixed_gptq" and cfgd["module_wbits"] == chosen
+
+
+@pytest.mark.parametrize("act", [False, True])
+def test_saved_model_round_trip(tmp_path, act):
+    """Quantize a tiny Llama, save it as safetensors + config.json, load it into a fresh model:
+    key names, dtypes and shapes follow the GPTQLinear layout and the logits are identical to
+    those of the model the driver left behind (dequantized weights in place)."""
+    import json
+
+    from safetensors.torch import load_file
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import run_quantize_with_qep_arch
+    from onecompression_b200.utils import load_quantized_layers, save_quantized_model
+
+    def fresh():
+        torch.manual_seed(3)
+        cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2,
+                          num_hidden_layers=2, vocab_size=512, max_position_embeddings=128,
+                          tie_word_embeddings=False)
+        return LlamaForCausalLM(cfg).half().to(DEV).eval()
+
+    model = fresh()
+    ids = torch.randint(0, 512, (32, 64), device=DEV)
+    q = GPTQ(wbits=4, groupsize=32, sym=False, actorder=act, mlp_wbits=3)
+    run_quantize_with_qep_arch(None, q, QEPConfig(device=DEV), None, model=model,
+                               model_inputs={"input_ids": ids}, report_progress=False)
+    model.to(DEV)            # the driver parks finished blocks on the host, as the reference does
+    with torch.no_grad():
+        want = model(input_ids=ids[:4]).logits.float().cpu()
+    save_quantized_model(model, q, str(tmp_path))
+    with torch.no_grad():
+        got = model(input_ids=ids[:4]).logits.float().cpu()
+    assert torch.equal(want, got)
+
+    tensors = load_file(str(tmp_path / "model.safetensors"))
+    name = "model.layers.1.mlp.down_proj"
+    assert name + ".weight" not in tensors
+    assert tensors[name + ".qweight"].dtype == torch.int32 and tuple(tensors[name + ".qweight"].shape) == (256 * 3 // 32, 128)
+    assert tensors[name + ".qzeros"].dtype == torch.int32 and tuple(tensors[name + ".qzeros"].shape) == (8, 128 * 3 // 32)
+    assert tensors[name + ".scales"].dtype == torch.float16 and tuple(tensors[name + ".scales"].shape) == (8, 128)
+    assert tensors[name + ".g_idx"].dtype == torch.int32 and tuple(tensors[name + ".g_idx"].shape) == (256,)
+    assert tuple(tensors["model.layers.0.self_attn.q_proj.qweight"].shape) == (128 * 4 // 32, 128)
+    qcfg = json.load(open(tmp_path / "config.json"))["quantization_config"]
+    assert qcfg["quant_method"] == "mixed_gptq" and qcfg["bits"] == 4 and qcfg["group_size"] == 32
+    assert qcfg["desc_act"] is act and qcfg["checkpoint_format"] == "gptq" and qcfg["mlp_wbits"] == 3
+    assert len(qcfg["quantization_bits"]) == 2
+    assert qcfg["quantization_bits"][1]["mlp.down_proj"] == {"bits": 3, "method": "gptq", "params": {"group_size": 32}}
+
+    again, _ = load_quantized_layers(fresh(), str(tmp_path))
+    with torch.no_grad():
+        got2 = again(input_ids=ids[:4]).logits.float().cpu()
+    assert torch.equal(want, got2)
