@@ -171,6 +171,20 @@ int oc_qep_adjust(void* W, long long ldw, int out, int d, const float* C, long l
 int oc_rmsnorm_f16(const void* x, long long ldx, const void* weight, float eps, long long rows, int d,
                    void* y, long long ldy, void* stream);
 
+/* Rotary position embedding of one tensor, y = x*cos + rotate_half(x)*sin with
+ * rotate_half(x) = cat(-x[D/2:], x[:D/2]) (the `apply_rotary_pos_emb` of the Llama / Qwen model
+ * code that the same block forwards run as six elementwise torch kernels).  x, y: fp16
+ * [B, H, S, D], element strides (xsb, xsh, xss, 1) and (ysb, ysh, yss, 1); cos, sin: fp16
+ * [B or 1, S, D], strides (cb, cs, 1) with cb = 0 for a broadcast batch.  D % 16 == 0.  Every
+ * product and the sum are rounded to fp16 separately, like the unfused operators. */
+int oc_rope_f16(const void* x, void* y, const void* cos, const void* sin, long long B, int H, int S, int D,
+                long long xsb, long long xsh, long long xss, long long ysb, long long ysh, long long yss,
+                long long cb, long long cs, int sm_count, void* stream);
+
+/* y = fp16(fp16(silu(gate)) * up) over n contiguous fp16 elements (y may alias gate): the
+ * `act_fn(gate_proj(x)) * up_proj(x)` of the gated MLP in the same block forwards. */
+int oc_swiglu_f16(const void* gate, const void* up, void* y, long long n, int sm_count, void* stream);
+
 /* ---- packed-layout utilities (onecomp/quantizer/gptq/gptq_layer.py:36-170) --------
  * pack_int_weights / unpack_int_weights: codes int32 [out, d] <-> qweight int32
  * [d*bits/32, out].  pack_zeros / unpack_zeros: zeros int32 [G, out] <-> qzeros int32

@@ -32,6 +32,8 @@ SIGNATURES = {
     "oc_qep_workspace_bytes": (_L, [_I, _I]),
     "oc_qep_adjust": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _F, _P, _L, _P]),
     "oc_rmsnorm_f16": (_I, [_P, _L, _P, _F, _L, _I, _P, _L, _P]),
+    "oc_rope_f16": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P]),
+    "oc_swiglu_f16": (_I, [_P, _P, _P, _L, _I, _P]),
     "oc_pack_qweight": (_I, [_P, _I, _I, _I, _P, _P]),
     "oc_unpack_qweight": (_I, [_P, _I, _I, _I, _P, _P]),
     "oc_pack_qzeros": (_I, [_P, _I, _I, _I, _I, _P, _P]),

@@ -31,6 +31,7 @@ SOURCES = {
     "qep.cu": [],
     "rtn.cu": ["-fmad=false"],
     "rmsnorm.cu": [],
+    "blockops.cu": ["-fmad=false"],
 }
 
 BASE = [

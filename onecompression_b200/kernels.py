@@ -468,6 +468,60 @@ def rmsnorm_f16(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tens
     return y.view(x.shape)
 
 
+def _dense(x: torch.Tensor) -> bool:
+    """True if x's elements occupy one gap-free block of memory without overlap (any dim order)."""
+    expect = 1
+    for size, stride in sorted(((sz, st) for sz, st in zip(x.shape, x.stride()) if sz != 1), key=lambda p: p[1]):
+        if stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+def rope_supported(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> bool:
+    """Whether ``rope_f16`` takes these tensors: fp16 CUDA, x [B, H, S, D] with unit last stride
+    and no overlap, cos / sin [B or 1, S, D] of equal strides, D a multiple of 16."""
+    if not (x.is_cuda and x.dtype == torch.float16 and x.dim() == 4 and x.stride(3) == 1):
+        return False
+    if cos.dim() != 3 or sin.shape != cos.shape or cos.dtype != torch.float16 or sin.dtype != torch.float16:
+        return False
+    if cos.stride() != sin.stride() or cos.stride(2) != 1 or cos.device != x.device or sin.device != x.device:
+        return False
+    b, _, s_len, d = x.shape
+    return (d % 16 == 0 and cos.shape[1] == s_len and cos.shape[2] == d and cos.shape[0] in (1, b)
+            and x.numel() > 0 and _dense(x))
+
+
+def rope_f16(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x*cos + rotate_half(x)*sin for x [B, H, S, D] (any dense layout) and cos / sin [B|1, S, D],
+    every operator rounded to fp16 like the unfused torch expression; the result has x's strides."""
+    if not rope_supported(x, cos, sin):
+        raise TypeError("rope_f16: unsupported tensors (see rope_supported)")
+    y = torch.empty_like(x)          # preserve_format: x's strides
+    if y.stride() != x.stride():
+        raise TypeError("rope_f16: could not allocate an output with the input's layout")
+    b, h, s_len, d = x.shape
+    cb = 0 if cos.shape[0] == 1 else cos.stride(0)
+    with torch.cuda.device(x.device):
+        call("oc_rope_f16", ptr(x), ptr(y), ptr(cos), ptr(sin), b, h, s_len, d, x.stride(0), x.stride(1),
+             x.stride(2), y.stride(0), y.stride(1), y.stride(2), cb, cos.stride(1), sm_count(x.device),
+             stream_handle())
+    return y
+
+
+def swiglu_f16(gate: torch.Tensor, up: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+    """fp16(fp16(silu(gate)) * up) for two contiguous fp16 tensors of equal shape; with
+    ``inplace`` the result overwrites ``gate``."""
+    _require_cuda(gate, "gate")
+    if (gate.dtype != torch.float16 or up.dtype != torch.float16 or gate.shape != up.shape
+            or not gate.is_contiguous() or not up.is_contiguous() or up.device != gate.device):
+        raise TypeError("swiglu_f16 expects two contiguous fp16 tensors of equal shape on one device")
+    y = gate if inplace else torch.empty_like(gate)
+    with torch.cuda.device(gate.device):
+        call("oc_swiglu_f16", ptr(gate), ptr(up), ptr(y), gate.numel(), sm_count(gate.device), stream_handle())
+    return y
+
+
 _staging = {"buf": None}
 
 

@@ -205,28 +205,125 @@ def _is_plain_rmsnorm(module) -> bool:
             and getattr(module, "weight", None) is not None and module.weight.dtype == torch.float16)
 
 
-class _FusedNorms:
-    """While active, plain RMSNorm modules of the given blocks run as one CUDA kernel."""
+_ROPE_BODY = (
+    "cos = cos.unsqueeze(unsqueeze_dim)",
+    "sin = sin.unsqueeze(unsqueeze_dim)",
+    "q_embed = (q * cos) + (rotate_half(q) * sin)",
+    "k_embed = (k * cos) + (rotate_half(k) * sin)",
+    "return q_embed, k_embed",
+)
+_ROTATE_HALF_BODY = (
+    "x1 = x[..., : x.shape[-1] // 2]",
+    "x2 = x[..., x.shape[-1] // 2 :]",
+    "return torch.cat((-x2, x1), dim=-1)",
+)
+_GATED_MLP_BODY = (
+    "down_proj = self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))",
+    "return down_proj",
+)
+_source_checks: dict = {}
 
-    def __init__(self, blocks, enabled=True):
-        self.mods = []
-        if enabled:
-            for b in blocks:
-                self.mods += [m for m in b.modules() if _is_plain_rmsnorm(m) and "forward" not in m.__dict__]
+
+def _code_lines(fn):
+    """Stripped source lines of ``fn`` without blank lines and comments ((), if unavailable)."""
+    import inspect
+
+    try:
+        src = inspect.getsource(inspect.unwrap(fn))
+    except (OSError, TypeError, ValueError):
+        return ()
+    return tuple(ln.strip() for ln in src.splitlines() if ln.strip() and not ln.strip().startswith("#"))
+
+
+def _ends_with(fn, body) -> bool:
+    key = (fn, body)
+    if key not in _source_checks:
+        lines = _code_lines(fn)
+        _source_checks[key] = len(lines) > len(body) and lines[-len(body):] == body
+    return _source_checks[key]
+
+
+def _is_plain_gated_mlp(module) -> bool:
+    """True for the gated MLP of Llama / Qwen blocks: down(act(gate(x)) * up(x)) with SiLU."""
+    if not all(hasattr(module, a) for a in ("gate_proj", "up_proj", "down_proj", "act_fn")):
+        return False
+    act = module.act_fn
+    silu = type(act) is nn.SiLU or (
+        isinstance(act, nn.Module) and "forward" not in act.__dict__
+        and _code_lines(type(act).forward)[-1:] == ("return nn.functional.silu(input)",))
+    return silu and _ends_with(type(module).forward, _GATED_MLP_BODY)
+
+
+def _plain_rope_namespace(module):
+    """The python module that defines ``module``'s class, if its ``apply_rotary_pos_emb`` and
+    ``rotate_half`` are, line for line, the Llama formulation; else None."""
+    import sys
+
+    ns = sys.modules.get(type(module).__module__)
+    fn, rot = getattr(ns, "apply_rotary_pos_emb", None), getattr(ns, "rotate_half", None)
+    if fn is None or rot is None or not callable(fn):
+        return None
+    head = [ln for ln in _code_lines(fn) if ln.startswith("def ")]
+    if not head or head[0] != "def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):":
+        return None
+    return ns if _ends_with(fn, _ROPE_BODY) and _ends_with(rot, _ROTATE_HALF_BODY) else None
+
+
+class _FusedOps:
+    """While active, elementwise chains of the given blocks run as single CUDA kernels with the
+    rounding points of the unfused operators: plain RMSNorm modules (``norms``), and the rotary
+    embedding and SwiGLU of Llama-style attention / MLP code (``elementwise``).  Anything whose
+    source differs from the recognised formulation, and any input the kernels do not take, runs
+    the model's own code."""
+
+    def __init__(self, blocks, norms=True, elementwise=True):
+        self.norm_mods, self.mlp_mods, self.rope_spaces = [], [], []
+        for b in blocks:
+            for m in b.modules():
+                if "forward" in m.__dict__:
+                    continue
+                if norms and _is_plain_rmsnorm(m):
+                    self.norm_mods.append(m)
+                elif elementwise and _is_plain_gated_mlp(m):
+                    self.mlp_mods.append(m)
+                if elementwise and hasattr(m, "q_proj") and hasattr(m, "k_proj"):
+                    ns = _plain_rope_namespace(m)
+                    if ns is not None and all(ns is not x for x, _ in self.rope_spaces):
+                        self.rope_spaces.append((ns, ns.apply_rotary_pos_emb))
 
     def __enter__(self):
-        for m in self.mods:
-            def fused(x, _m=m):
+        for m in self.norm_mods:
+            def fused_norm(x, _m=m):
                 if x.is_cuda and x.dtype == torch.float16:
                     return kernels.rmsnorm_f16(x, _m.weight, _m.variance_epsilon)
                 return type(_m).forward(_m, x)
 
-            m.forward = fused
+            m.forward = fused_norm
+        for m in self.mlp_mods:
+            def fused_mlp(x, _m=m):
+                gate, up = _m.gate_proj(x), _m.up_proj(x)
+                if (gate.is_cuda and gate.dtype == torch.float16 and up.dtype == torch.float16
+                        and gate.shape == up.shape and gate.is_contiguous() and up.is_contiguous()):
+                    # not in place: a memoised gate_proj hands out views of its record
+                    return _m.down_proj(kernels.swiglu_f16(gate, up))
+                return _m.down_proj(_m.act_fn(gate) * up)
+
+            m.forward = fused_mlp
+        for ns, original in self.rope_spaces:
+            def fused_rope(q, k, cos, sin, unsqueeze_dim=1, _orig=original, **kw):
+                if (unsqueeze_dim == 1 and not kw and kernels.rope_supported(q, cos, sin)
+                        and kernels.rope_supported(k, cos, sin)):
+                    return kernels.rope_f16(q, cos, sin), kernels.rope_f16(k, cos, sin)
+                return _orig(q, k, cos, sin, unsqueeze_dim, **kw)
+
+            ns.apply_rotary_pos_emb = fused_rope
         return self
 
     def __exit__(self, *exc):
-        for m in self.mods:
+        for m in self.norm_mods + self.mlp_mods:
             m.__dict__.pop("forward", None)
+        for ns, original in self.rope_spaces:
+            ns.apply_rotary_pos_emb = original
         return False
 
 
@@ -340,11 +437,12 @@ class BlockQuantizer:
 
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
                  dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True,
-                 profile: bool = False, fuse_rmsnorm: bool = True):
+                 profile: bool = False, fuse_rmsnorm: bool = True, fuse_elementwise: bool = True):
         self.memoize = memoize
         # Llama-style RMSNorm modules of the block run as one kernel during the passes (same
         # rounding points as the module; the row sum is formed in another order)
         self.fuse_rmsnorm = fuse_rmsnorm
+        self.fuse_elementwise = fuse_elementwise
         # with profile=True every phase is bracketed by device synchronisation and its wall
         # time is added to self.timings (seconds per phase name); off by default
         self.profile = profile
@@ -435,7 +533,7 @@ class BlockQuantizer:
                 handles.append(mods_f[head].register_forward_pre_hook(make(head)))
         next_f = torch.empty_like(inps_f)
         try:
-            with _FusedNorms([block_f], self.fuse_rmsnorm):
+            with _FusedOps([block_f], self.fuse_rmsnorm, self.fuse_elementwise):
                 for first in range(0, n_seq, bs):
                     cursor["first"] = first
                     y = call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
@@ -493,7 +591,7 @@ class BlockQuantizer:
         use_cache = fp["use_cache"]
         if next_block is not None and not self.profile:
             self.prefetch(next_block, next_f, kwargs)
-        with _FusedNorms([block_q, block_f], self.fuse_rmsnorm):
+        with _FusedOps([block_q, block_f], self.fuse_rmsnorm, self.fuse_elementwise):
             return self._run_quantized(block_q, inps_q, inps_f, kwargs, on_layer_done, fp, t0)
 
     def _run_quantized(self, block_q, inps_q, inps_f, kwargs, on_layer_done, fp, t0):

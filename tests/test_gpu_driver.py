@@ -544,3 +544,36 @@ def test_saved_model_round_trip(tmp_path, act):
     with torch.no_grad():
         got2 = again(input_ids=ids[:4]).logits.float().cpu()
     assert torch.equal(want, got2)
+
+
+def test_fused_block_ops_change_nothing():
+    """Rotary embedding, SwiGLU and RMSNorm fused into single kernels: the block passes, and with
+    them every quantized layer, are bit-identical to the model's own elementwise code for rotary
+    and SwiGLU (RMSNorm orders its row sum differently and is held to one fp16 ulp elsewhere)."""
+    from onecompression_b200 import GPTQ, QEPConfig, synthetic
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer, _FusedOps
+
+    shape = dict(synthetic.LLAMA3_8B, hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=64, vocab_size=1000)
+    stack = synthetic.llama_blocks(shape, 1, 64, DEV, seed=6)
+    blk = stack.blocks[0]
+    found = _FusedOps([blk])
+    assert len(found.norm_mods) == 2 and len(found.mlp_mods) == 1 and len(found.rope_spaces) == 1
+    outs = []
+    for fuse in (False, True):
+        stack = synthetic.llama_blocks(shape, 1, 64, DEV, seed=6)
+        x0 = synthetic.embedded_tokens(1000, 256, 40, 64, DEV, seed=6) * 30
+        q = GPTQ(wbits=4, groupsize=128, sym=True)
+        for n, m in stack.blocks[0].named_modules():
+            if isinstance(m, torch.nn.Linear):
+                q.module_to_name[m] = f"model.layers.0.{n}"
+        runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV, fuse_rmsnorm=False,
+                                fuse_elementwise=fuse)
+        nq, nf = runner.run(stack.blocks[0], x0.clone(), x0.clone(), stack.kwargs)
+        outs.append((nq.cpu(), nf.cpu(), {k: (r.qweight, r.scales, r.qzeros) for k, r in q.results.items()}))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for k in outs[0][2]:
+        for a, b in zip(outs[0][2][k], outs[1][2][k]):
+            assert torch.equal(a, b), k
+    import transformers.models.llama.modeling_llama as ml
+    assert ml.apply_rotary_pos_emb.__name__ == "apply_rotary_pos_emb"      # the patch is undone

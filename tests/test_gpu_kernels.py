@@ -351,3 +351,36 @@ def test_rmsnorm_matches_module_formula(K, rows, d):
     b = want.cpu().numpy().view(np.uint16).astype(np.int64)
     assert np.abs(a - b).max() <= 1                 # same rounding points; the row sum is ordered differently
     assert (a == b).mean() > 0.999
+
+
+# ---- fused rotary embedding and SwiGLU of the block passes -------------------------------------------------
+
+@pytest.mark.parametrize("b,h,s,d,bcast", [(3, 8, 64, 128, True), (2, 4, 33, 64, False), (1, 2, 7, 32, True)])
+def test_rope_is_bit_identical_to_the_model_code(K, b, h, s, d, bcast):
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+
+    g = torch.Generator().manual_seed(b * 100 + d)
+    proj = (torch.randn(b, s, h * d, generator=g) * 2).half().to(dev())
+    q = proj.view(b, s, h, d).transpose(1, 2)                       # the layout attention code produces
+    ang = torch.rand(1 if bcast else b, s, d, generator=g) * 6.28
+    cos, sin = ang.cos().half().to(dev()), ang.sin().half().to(dev())
+    want, _ = apply_rotary_pos_emb(q, q, cos, sin)
+    assert K.rope_supported(q, cos, sin)
+    got = K.rope_f16(q, cos, sin)
+    assert got.stride() == want.stride() == q.stride()
+    assert torch.equal(got, want)
+    qc = q.contiguous()                                             # a different memory order
+    assert torch.equal(K.rope_f16(qc, cos, sin), want)
+    assert not K.rope_supported(q.float(), cos, sin) and not K.rope_supported(q[..., :24], cos[..., :24], sin[..., :24])
+
+
+@pytest.mark.parametrize("shape", [(4, 64, 1024), (3, 5, 250), (1, 1, 7)])
+def test_swiglu_is_bit_identical_to_the_model_code(K, shape):
+    g = torch.Generator().manual_seed(shape[-1])
+    gate = (torch.randn(*shape, generator=g) * 4).half().to(dev())
+    up = (torch.randn(*shape, generator=g) * 2).half().to(dev())
+    gate.view(-1)[:4] = torch.tensor([0.0, -0.0, 65504.0, -65504.0], dtype=torch.float16)
+    want = torch.nn.functional.silu(gate) * up
+    assert torch.equal(K.swiglu_f16(gate, up), want)
+    g2 = gate.clone()
+    assert K.swiglu_f16(g2, up, inplace=True).data_ptr() == g2.data_ptr() and torch.equal(g2, want)
