@@ -56,12 +56,14 @@ long long oc_launch_count_reset(void);
  * triangle: call oc_mirror_upper(H) once after the last accumulation.  C is
  * written in full.  Any other shape runs an fp32 FMA kernel that writes H in full.
  * chunk_tokens (0 = 512): tokens per tensor-core accumulation chain.
- * sm_count: CTAs to launch at most (0 = 148).  force_simt: 1 selects the FMA kernel.
- * status: 0, or 101..104 when a bounded pipeline wait expired (result invalid).
+ * sm_count: CTAs to launch at most (0 = 148).
+ * engine: 0 = automatic, 1 = the FMA kernel, 2 = tensor cores with one CTA per 128 x 256 tile,
+ * 3 = tensor cores with one CTA pair (cta_group::2) per 256 x 256 tile.
+ * status: 0, or 101..104 / 201..204 when a bounded pipeline wait expired (result invalid).
  */
 int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok, int d,
                     long long ld, float* H, float* C, long long ldh, float a_old, float a_new,
-                    int chunk_tokens, int sm_count, int force_simt, int* status, void* stream);
+                    int chunk_tokens, int sm_count, int engine, int* status, void* stream);
 
 /* Same computation as oc_moment_accum for callers that cannot allocate device memory (no
  * counterpart in the reference, which allocates freely through torch).  A host that runs

@@ -26,6 +26,7 @@ SOURCES = {
     "gptq.cu": ["-fmad=false"],
     "moment_simt.cu": [],
     "moment_tc.cu": [],
+    "moment_tc2.cu": [],
     "moment_noalloc.cu": [],
     "pack.cu": [],
     "qep.cu": [],

@@ -44,6 +44,17 @@ void oc_count_launches(int n);
 
 static inline int oc_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 
+// ---- engines of oc_moment_accum (its `engine` argument) ---------------------
+enum : int {
+  OC_MOMENT_AUTO = 0,    // tensor cores when the shapes allow, else FMA
+  OC_MOMENT_SIMT = 1,    // fp32 FMA kernel
+  OC_MOMENT_SINGLE = 2,  // tcgen05, one CTA per 128 x 256 tile
+  OC_MOMENT_PAIR = 3,    // tcgen05 cta_group::2, one CTA pair per 256 x 256 tile
+};
+#ifndef OC_MOMENT_AUTO_USES_PAIRS
+#define OC_MOMENT_AUTO_USES_PAIRS 0
+#endif
+
 // ---- fp32 GEMM engine (gemm.cu) -------------------------------------------
 // C[M,N] = beta*C + alpha * opA(A) * opB(B), all fp32, exact FMA arithmetic.
 //   transA = 0: A is [M,K] row-major (lda);  1: A is [K,M] row-major.

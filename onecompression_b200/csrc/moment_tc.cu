@@ -198,11 +198,11 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + half * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(taddr + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          float v[64];
+          tmem_ld64(taddr + c * 64, v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+          for (int i = 0; i < 64; ++i) acc[c * 64 + i] += v[i];
         }
         tc_fence_before();
         __syncwarp();
@@ -261,15 +261,19 @@ int oc_moment_simt_launch(const __half* xq, const __half* xf, long long n_tok, i
 
 int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, cudaStream_t stream);
 
+int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delta, float* H, float* C,
+                          long long ldh, int d, long long n_tok, float a_old, float a_new, int chunk_tokens,
+                          int sm_count, int* status, cudaStream_t stream);
+
 // See include/onecomp_b200.h for the contract.
 extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok,
                                int d, long long ld, float* H, float* C, long long ldh, float a_old,
-                               float a_new, int chunk_tokens, int sm_count, int force_simt,
+                               float a_new, int chunk_tokens, int sm_count, int engine,
                                int* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   OC_REQUIRE(xq && (H || C) && d > 0 && n_tok >= 0 && ld >= d && ldh >= d, "moment_accum: bad arguments");
   OC_REQUIRE(!C || xf, "moment_accum: the cross term needs the full-precision activations");
-  const bool tc_ok = !force_simt && d % 8 == 0 && ld % 8 == 0 && ldh % 4 == 0 && n_tok > 0 && status &&
+  const bool tc_ok = engine != OC_MOMENT_SIMT && d % 8 == 0 && ld % 8 == 0 && ldh % 4 == 0 && n_tok > 0 && status &&
                      ((uintptr_t)xq & 15) == 0 && (!C || (delta_scratch && ((uintptr_t)delta_scratch & 15) == 0)) &&
                      (!H || ((uintptr_t)H & 15) == 0) && (!C || ((uintptr_t)C & 15) == 0);
   if (!tc_ok) {
@@ -288,6 +292,10 @@ extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scrat
   if (rc) return rc;
   if (C) { rc = make_map(&map_delta, delta_or_xf, n_tok, d, ld); if (rc) return rc; }
   else map_delta = map_xq;
+
+  if (engine == OC_MOMENT_PAIR || (engine == OC_MOMENT_AUTO && OC_MOMENT_AUTO_USES_PAIRS))
+    return oc_moment_pair_launch(map_xq, map_delta, H, C, ldh, d, n_tok, a_old, a_new, chunk_tokens, sm_count,
+                                 status, stream);
 
   MomentParams p{};
   p.H = H; p.C = C; p.ldh = ldh; p.d = d; p.n_tok = n_tok; p.a_old = a_old; p.a_new = a_new;

@@ -54,8 +54,10 @@ class MomentAccumulator:
     the moments are scaled by n/(n+t), then the chunk enters with weight 2/(n+t).
     """
 
+    ENGINES = {"auto": 0, "simt": 1, "single": 2, "pair": 3}
+
     def __init__(self, d: int, device, cross: bool = False, chunk_tokens: int = 0,
-                 force_simt: bool = False):
+                 force_simt: bool = False, engine: str = "auto"):
         self.d = d
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -67,7 +69,8 @@ class MomentAccumulator:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the tensor-core kernel needs 16-byte rows; decide once so that every chunk of
         # one accumulation takes the same path
-        self.force_simt = bool(force_simt) or d % 8 != 0
+        self.force_simt = bool(force_simt) or d % 8 != 0 or engine == "simt"
+        self.engine = 1 if self.force_simt else self.ENGINES[engine]
         self._scratch = None
         self._needs_mirror = False
 
@@ -99,7 +102,7 @@ class MomentAccumulator:
             call(
                 "oc_moment_accum", ptr(xq), ptr(xf) if cross else None, ptr(scratch), t, self.d,
                 xq.stride(0), ptr(self.H), ptr(self.C), self.d, a_old, a_new, self.chunk_tokens,
-                sm_count(self.device), 1 if self.force_simt else 0, ptr(self.status), stream_handle(),
+                sm_count(self.device), self.engine, ptr(self.status), stream_handle(),
             )
         self._needs_mirror = not self.force_simt
 

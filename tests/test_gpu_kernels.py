@@ -144,14 +144,15 @@ def test_moments_match_reference_vectors(K, simt):
     assert torch.equal(h2, h2.t())
 
 
+@pytest.mark.parametrize("engine", ["single", "pair"])
 @pytest.mark.parametrize("d,ntok,chunk", [(512, 8192, 0), (2880, 4096, 1024), (1000, 3000, 0), (264, 100, 0)])
-def test_hessian_tensor_core_vs_float64(K, d, ntok, chunk):
+def test_hessian_tensor_core_vs_float64(K, d, ntok, chunk, engine):
     g = torch.Generator().manual_seed(d)
     x = torch.randn(ntok, d, generator=g)
     x[:, torch.randperm(d, generator=g)[:8]] *= 20
     x = x.half()
     want = (2.0 / ntok) * (x.double().t() @ x.double())
-    acc = K.MomentAccumulator(d, dev(), chunk_tokens=chunk)
+    acc = K.MomentAccumulator(d, dev(), chunk_tokens=chunk, engine=engine)
     for part in x.to(dev()).split(ntok // 2 + 7):
         acc.add(part)
     h, _, n = acc.finalize()
@@ -160,14 +161,31 @@ def test_hessian_tensor_core_vs_float64(K, d, ntok, chunk):
     assert torch.equal(h, h.t())
 
 
-def test_cross_term_tensor_core_vs_float64(K):
+def test_pair_engine_equals_single_engine_bit_for_bit(K):
+    """Both tensor-core engines add the same products in the same order (512-token chains, fp32
+    sums of the chains), so their results are identical."""
+    g = torch.Generator().manual_seed(11)
+    d, ntok = 1536, 5000
+    xf = torch.randn(ntok, d, generator=g).half().to(dev())
+    xq = (xf.float() * 1.01).half()
+    out = {}
+    for engine in ("single", "pair"):
+        acc = K.MomentAccumulator(d, dev(), cross=True, engine=engine)
+        for a, b in zip(xq.split(2048), xf.split(2048)):
+            acc.add(a, b)
+        out[engine] = acc.finalize()
+    assert torch.equal(out["single"][0], out["pair"][0]) and torch.equal(out["single"][1], out["pair"][1])
+
+
+@pytest.mark.parametrize("engine", ["single", "pair"])
+def test_cross_term_tensor_core_vs_float64(K, engine):
     g = torch.Generator().manual_seed(3)
     d, ntok = 768, 4096
     xf = torch.randn(ntok, d, generator=g).half()
     xq = (xf.float() * (1 + 0.03 * torch.randn(ntok, d, generator=g))).half()
     want_c = (2.0 / ntok) * ((xf.double() - xq.double()).t() @ xq.double())
     want_h = (2.0 / ntok) * (xq.double().t() @ xq.double())
-    acc = K.MomentAccumulator(d, dev(), cross=True)
+    acc = K.MomentAccumulator(d, dev(), cross=True, engine=engine)
     acc.add(xq.to(dev()), xf.to(dev()))
     h, c, _ = acc.finalize()
     assert _rel(h.cpu(), want_h) < 1e-5
