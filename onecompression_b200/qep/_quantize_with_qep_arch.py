@@ -437,12 +437,14 @@ class BlockQuantizer:
 
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
                  dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True,
-                 profile: bool = False, fuse_rmsnorm: bool = True, fuse_elementwise: bool = True):
+                 profile: bool = False, fuse_rmsnorm: bool = True, fuse_elementwise: bool = True,
+                 stack_layers: bool = True):
         self.memoize = memoize
         # Llama-style RMSNorm modules of the block run as one kernel during the passes (same
         # rounding points as the module; the row sum is formed in another order)
         self.fuse_rmsnorm = fuse_rmsnorm
         self.fuse_elementwise = fuse_elementwise
+        self.stack_layers = stack_layers
         # with profile=True every phase is bracketed by device synchronisation and its wall
         # time is added to self.timings (seconds per phase name); off by default
         self.profile = profile
@@ -652,6 +654,7 @@ class BlockQuantizer:
                 h, c, n = self.dist.reduce_moments(h, c, n)
                 t0 = self._tick("allreduce", t0)
             factors = {}
+            plan = []            # [(modules sharing one call, factor, excluded)]
             for module in group:
                 name = qz.module_to_name.get(module)
                 if name is None:
@@ -665,12 +668,37 @@ class BlockQuantizer:
                         t0 = self._tick("factor", t0)
                     factor = factors[key]
                 excluded = self._excluded(name)
-                self._quantize_one(module, name, h, None if excluded else c, n, factor)
-                if memo is not None:
-                    memo.mark_done(module)
+                skey = None
+                if child is not None and self.stack_layers and self.dist is None:
+                    skey = child.stack_key(module)
+                    if skey is not None:
+                        skey = skey + (excluded,)
+                for entry in plan:
+                    if skey is not None and entry["key"] == skey:
+                        entry["modules"].append(module)
+                        break
+                else:
+                    plan.append({"key": skey, "modules": [module], "factor": factor, "excluded": excluded,
+                                 "child": child})
+            for entry in plan:
+                mods, excluded = entry["modules"], entry["excluded"]
+                if len(mods) > 1:
+                    results = entry["child"].quantize_stacked(
+                        mods, h, entry["factor"], None if excluded else c, self.cfg.percdamp, self.cfg.perccorr)
+                    for module in mods:
+                        name = qz.module_to_name[module]
+                        qz.results[name] = results[module]
+                        self._install_dequantized(module, name)
+                else:
+                    name = qz.module_to_name[mods[0]]
+                    self._quantize_one(mods[0], name, h, None if excluded else c, n, entry["factor"])
                 t0 = self._tick("correct+quantize", t0)
-                if on_layer_done is not None:
-                    on_layer_done(f"{name}, no weight correction" if excluded else name)
+                for module in mods:
+                    name = qz.module_to_name[module]
+                    if memo is not None:
+                        memo.mark_done(module)
+                    if on_layer_done is not None:
+                        on_layer_done(f"{name}, no weight correction" if excluded else name)
 
         if experts:
             per_module = _compute_per_module_hessians(block_q, experts, inps_q, kwargs, bs, dev, self.dist)

@@ -296,6 +296,87 @@ class GPTQ(Quantizer):
         result.__dict__["_device_dequantized"] = dev_out["dequantized"]
         return result
 
+    # ------------------------------------------------------------------ several layers, one input
+
+    def stack_key(self, module):
+        """Layers with equal keys (and one shared input, hence one Hessian) may be quantized as one
+        stacked weight matrix: rows never interact in GPTQ or in the QEP correction, so stacking
+        changes no result.  None when the layer cannot take part."""
+        if (type(self).quantize_with_qep is not Quantizer.quantize_with_qep
+                or type(self).quantize_layer is not GPTQ.quantize_layer):
+            return None          # a subclass that hooks the per-layer calls gets per-layer calls
+        name = self.module_to_name.get(module)
+        w = getattr(module, "weight", None)
+        if (name is None or type(module) is not torch.nn.Linear or w is None or not w.is_cuda
+                or w.dtype != torch.float16 or w.shape[0] % 32 != 0 or self.calc_quant_error):
+            return None
+        bits = GPTQ.resolve_bits(name, self.wbits, self.mlp_wbits, self.module_wbits)
+        gs = GPTQ.resolve_groupsize(name, self.groupsize, self.mlp_groupsize)
+        if self.bitpack_on_quantize and not is_packable_wbits(bits):
+            return None
+        return (id(self), bits, gs, w.shape[1], w.device)
+
+    def quantize_stacked(self, modules, hessian, factor, delta_hatX=None, percdamp=0.01, perccorr=0.5):
+        """``quantize_with_qep`` for several layers that share ``hessian`` (equal ``stack_key``):
+        one correction and one column loop over the row-wise concatenation of their weights.
+        Returns {module: GPTQResult}; results are identical to the per-layer calls."""
+        import time
+
+        t0 = time.time()
+        first = modules[0]
+        name0 = self.module_to_name[first]
+        bits = GPTQ.resolve_bits(name0, self.wbits, self.mlp_wbits, self.module_wbits)
+        gs = GPTQ.resolve_groupsize(name0, self.groupsize, self.mlp_groupsize)
+        stacked = torch.cat([m.weight.data for m in modules], dim=0)
+        rows = [m.weight.shape[0] for m in modules]
+        if delta_hatX is not None:
+            from .._quantizer import _qep_shift_rule
+
+            fac = factor
+            if not (fac.attempts == 1 and abs(fac.percdamp - percdamp) < 1e-12 and not fac.actorder):
+                fac = kernels.factor_hessian(hessian, percdamp, actorder=False, shifts=_qep_shift_rule())
+            kernels.qep_adjust(stacked, delta_hatX.to(stacked.device), fac, perccorr)
+            r0 = 0
+            for m, r in zip(modules, rows):        # the corrected weight is the module's weight now
+                m.weight.data.copy_(stacked[r0:r0 + r])
+                r0 += r
+        packed = self.bitpack_on_quantize
+        out = kernels.gptq_quantize(
+            stacked, factor, wbits=bits, groupsize=gs, sym=self.sym, blocksize=self.blocksize, pack=packed,
+            want_codes=not packed, want_dequantized=True, mse=bool(self.mse), q_grid=self.q_grid,
+            q_norm=self.q_norm,
+        )
+        d = stacked.shape[1]
+        perm = factor.perm.to(torch.int64) if self.actorder else None
+        pieces, r0 = [], 0
+        for r in rows:
+            if packed:
+                pieces += [out["qweight"][:, r0:r0 + r], out["qzeros"][:, r0 * bits // 32:(r0 + r) * bits // 32]]
+            else:
+                pieces += [out["codes"][r0:r0 + r], out["zeros"][:, r0:r0 + r]]
+            pieces.append(out["scales"][:, r0:r0 + r])
+            r0 += r
+        host = kernels.to_host(pieces + [perm])
+        perm_host = host[-1]
+        elapsed = time.time() - t0
+        results, r0 = {}, 0
+        for i, (m, r) in enumerate(zip(modules, rows)):
+            qweight, qzeros, scales = host[3 * i], host[3 * i + 1], host[3 * i + 2]
+            if gs == -1:
+                scales = scales.reshape(r, 1)
+                if not packed:
+                    qzeros = qzeros.reshape(r, 1)
+            res = GPTQResult(
+                wbits=bits, groupsize=gs, actorder=self.actorder, sym=self.sym, qweight=qweight, scales=scales,
+                qzeros=qzeros, perm=perm_host.clone() if perm_host is not None else None,
+                qweight_is_packed=packed, qzeros_is_packed=packed, qweight_original_shape=(r, d),
+            )
+            res.__dict__["_device_dequantized"] = out["dequantized"][r0:r0 + r]
+            res.quantization_time = elapsed * r / sum(rows)
+            results[m] = res
+            r0 += r
+        return results
+
     # ------------------------------------------------------------------ save-side metadata
 
     def get_quant_config(self) -> dict:

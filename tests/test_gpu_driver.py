@@ -577,3 +577,35 @@ def test_fused_block_ops_change_nothing():
             assert torch.equal(a, b), k
     import transformers.models.llama.modeling_llama as ml
     assert ml.apply_rotary_pos_emb.__name__ == "apply_rotary_pos_emb"      # the patch is undone
+
+
+@pytest.mark.parametrize("bits,gs,sym,act,pack", [(4, 128, True, False, True), (3, 64, False, True, True),
+                                                  (5, -1, True, False, False)])
+def test_stacked_layers_change_nothing(bits, gs, sym, act, pack):
+    """Layers that share an input (q/k/v, gate/up) quantized as one stacked weight matrix: every
+    result and both propagated activations are bit-identical to the layer-by-layer run."""
+    from onecompression_b200 import GPTQ, QEPConfig, synthetic
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+
+    shape = dict(synthetic.LLAMA3_8B, hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=64, vocab_size=1000)
+    outs = []
+    for stack_layers in (False, True):
+        stack = synthetic.llama_blocks(shape, 1, 64, DEV, seed=8)
+        x0 = synthetic.embedded_tokens(1000, 256, 40, 64, DEV, seed=8) * 30
+        q = GPTQ(wbits=bits, groupsize=gs, sym=sym, actorder=act, bitpack_on_quantize=pack)
+        for n, m in stack.blocks[0].named_modules():
+            if isinstance(m, torch.nn.Linear):
+                q.module_to_name[m] = f"model.layers.0.{n}"
+        runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV, stack_layers=stack_layers)
+        nq, nf = runner.run(stack.blocks[0], x0.clone(), x0.clone(), stack.kwargs)
+        outs.append((nq.cpu(), nf.cpu(), {k: (r.qweight, r.scales, r.qzeros, r.perm, r.qweight_original_shape,
+                                              r.quantization_time) for k, r in q.results.items()}))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert set(outs[0][2]) == set(outs[1][2]) and len(outs[0][2]) == 7
+    for k in outs[0][2]:
+        a, b = outs[0][2][k], outs[1][2][k]
+        for x, y in zip(a[:3], b[:3]):
+            assert x.dtype == y.dtype and x.shape == y.shape and torch.equal(x, y), k
+        assert (a[3] is None and b[3] is None) or torch.equal(a[3], b[3])
+        assert a[4] == b[4] and b[5] > 0
