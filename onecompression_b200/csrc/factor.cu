@@ -5,7 +5,7 @@
 // Cholesky factorisation and one triangular inverse:
 //
 //   A = J (P H P^T + damp I) J      (J reverses the index order, P is the act-order permutation)
-//   A = L L^T                       blocked right-looking Cholesky, fp32
+//   A = L L^T                       blocked right-looking Cholesky (two levels: 128 / 512), fp32
 //   X = L^-1                        recursive blocked triangular inverse, fp32
 //   U = J X J                       upper triangular, U^T U = (P H P^T + damp I)^-1
 //
@@ -15,6 +15,7 @@
 namespace {
 
 constexpr int NB = 128;  // panel width
+constexpr int OB = 512;  // outer block of the two-level Cholesky
 
 // ---- diag statistics: dead columns, damping --------------------------------
 // diagv[j] = H[j,j] (1 where it is 0), dead[j], damp_out[0] = percdamp * mean(diagv)
@@ -102,25 +103,28 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
 // A non-positive or non-finite pivot records (global index + 1) in *status (first one wins)
 // and continues with pivot 1 so that every later kernel still terminates.
 //
-// Factorisation: 16 x 16 threads, each holding an 8 x 8 sub-block in registers; per column one
-// thread takes the square root, the 16 threads of that block column scale it and publish it, and
-// every thread below the diagonal applies the rank-1 update to its registers (two barriers per
-// column).  Inverse: block forward substitution, 8 rows at a time; each thread owns one column
+// Factorisation: 16 x 16 threads, each holding an 8 x 8 sub-block in registers.  The eight
+// columns of a micro-panel are finished inside the one warp that holds that block column
+// (shuffles only), published to shared memory, and every thread to the right applies them as
+// eight rank-1 updates to its registers: one barrier per eight columns.  Inverse: block forward substitution, 8 rows at a time; each thread owns one column
 // (two threads share a column and split the inner dimension).
 __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
                                                          float* __restrict__ X, long long ldx,
                                                          int k0, int nb, int* __restrict__ status) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
   float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
   float* colbuf = sm + 2 * NB * (NB + 1);                                          // [128]
   float (*P)[8][NB] = reinterpret_cast<float (*)[8][NB]>(colbuf + NB);             // [2][8][128]
   float (*D)[8] = reinterpret_cast<float (*)[8]>(colbuf + NB + 2 * 8 * NB);        // [8][8]
-  __shared__ float pivot;
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // block column tx of the 16 x 16 grid of 8 x 8 register blocks lives in one half-warp
+  const int tid = threadIdx.x, tx = tid >> 4, ty = tid & 15;
   const int r0 = ty * 8, c0 = tx * 8;
   float* Ab = A + (long long)k0 * lda + k0;
   float* Xb = X + (long long)k0 * ldx + k0;
+  // L of the current 8-column micro-panel, column-major [8][128], double buffered; it overlays
+  // Y, which is not used before the inverse phase
+  float (*Lp)[8][NB + 4] = reinterpret_cast<float (*)[8][NB + 4]>(&Y[0][0]);
 
   float a[8][8];
 #pragma unroll
@@ -132,43 +136,69 @@ __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, 
     }
 
   for (int jb = 0; jb < NB / 8; ++jb) {
+    const int buf = jb & 1;
+    if ((tid >> 5) == (jb >> 1)) {
+      // ---- the micro-panel's eight columns inside one warp (shuffles, no barrier) ----
+      const int pl = ((jb & 1) << 4) + jb;          // lane that owns the diagonal 8 x 8 block
+      const bool mine = (tx == jb) && (ty >= jb);
+      const bool is_pivot = (tx == jb) && (ty == jb);
 #pragma unroll
-    for (int jj = 0; jj < 8; ++jj) {
-      const int j = jb * 8 + jj;
-      if (ty == jb && tx == jb) {
-        float p = a[jj][jj];
+      for (int jj = 0; jj < 8; ++jj) {
+        float p = __shfl_sync(0xffffffffu, a[jj][jj], pl);
         if (!(p > 0.f) || !isfinite(p)) {
-          atomicCAS(status, 0, k0 + j + 1);
+          if (is_pivot) atomicCAS(status, 0, k0 + jb * 8 + jj + 1);
           p = 1.f;
         }
-        p = sqrtf(p);
-        a[jj][jj] = p;
-        pivot = p;
-      }
-      __syncthreads();
-      if (tx == jb && ty >= jb) {
-        const float inv = 1.f / pivot;
+        // the only serial arithmetic of a column step: one approximate reciprocal square root,
+        // refined once, instead of an IEEE square root followed by an IEEE division
+        float inv = rsqrtf(p);
+        inv = inv * fmaf(-0.5f * p * inv, inv, 1.5f);
+        const float piv = p * inv;
+        if (is_pivot) a[jj][jj] = piv;
+        if (mine) {
 #pragma unroll
-        for (int ii = 0; ii < 8; ++ii) {
-          if (r0 + ii > j) {
-            a[ii][jj] *= inv;
-            colbuf[r0 + ii] = a[ii][jj];
+          for (int ii = 0; ii < 8; ++ii)
+            if (!is_pivot || ii > jj) a[ii][jj] *= inv;
+        }
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          if (cc <= jj) continue;
+          const float lc = __shfl_sync(0xffffffffu, a[cc][jj], pl);   // L[8 jb + cc][8 jb + jj]
+          if (mine) {
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii)
+              if (!is_pivot || ii >= cc) a[ii][cc] = fmaf(-a[ii][jj], lc, a[ii][cc]);
           }
         }
       }
-      __syncthreads();
-      if (ty >= tx && tx >= jb) {
-        float rc[8], cv[8];
+      if (mine) {
 #pragma unroll
-        for (int t = 0; t < 8; ++t) { rc[t] = colbuf[r0 + t]; cv[t] = colbuf[c0 + t]; }
+        for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+          for (int ii = 0; ii < 8; ++ii) Lp[buf][jj][r0 + ii] = a[ii][jj];
+      }
+    }
+    __syncthreads();
+    // ---- rank-8 update of everything to the right, one column of the panel at a time, in
+    // the order of eight successive rank-1 updates ----
+    if (tx > jb && ty >= tx) {
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const float4 r_lo = *reinterpret_cast<const float4*>(&Lp[buf][jj][r0]);
+        const float4 r_hi = *reinterpret_cast<const float4*>(&Lp[buf][jj][r0 + 4]);
+        const float4 c_lo = *reinterpret_cast<const float4*>(&Lp[buf][jj][c0]);
+        const float4 c_hi = *reinterpret_cast<const float4*>(&Lp[buf][jj][c0 + 4]);
+        const float rc[8] = {r_lo.x, r_lo.y, r_lo.z, r_lo.w, r_hi.x, r_hi.y, r_hi.z, r_hi.w};
+        const float cv[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
 #pragma unroll
         for (int ii = 0; ii < 8; ++ii)
 #pragma unroll
           for (int cc = 0; cc < 8; ++cc)
-            if (c0 + cc > j && r0 + ii >= c0 + cc) a[ii][cc] = fmaf(-rc[ii], cv[cc], a[ii][cc]);
+            if (ty > tx || ii >= cc) a[ii][cc] = fmaf(-rc[ii], cv[cc], a[ii][cc]);
       }
     }
   }
+  __syncthreads();          // Lp overlays Y: everyone is done with it before S / Y are written
 #pragma unroll
   for (int ii = 0; ii < 8; ++ii)
 #pragma unroll
@@ -292,28 +322,47 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
     OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  for (int k0 = 0; k0 < n; k0 += NB) {
-    const int nb = min(NB, n - k0);
-    potrf_diag_kernel<<<1, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status);
-    OC_CHECK_LAUNCH();
-    const int rest = n - k0 - nb;
-    if (rest <= 0) break;
-    float* panel = A + (long long)(k0 + nb) * ld + k0;
-    OcGemm g{};
-    // panel <- panel * (Lkk^-1)^T  (in place: one column tile, every CTA reads its rows first)
-    g.A = panel; g.lda = ld; g.B = X + (long long)k0 * ld + k0; g.ldb = ld; g.C = panel; g.ldc = ld;
-    g.M = rest; g.N = nb; g.K = nb; g.alpha = 1.f; g.beta = 0.f; g.transA = 0; g.transB = 1;
-    g.flags = 0; g.batch = 1;
-    int rc = oc_gemm_f32_launch(g, stream);
-    if (rc) return rc;
-    // trailing <- trailing - panel * panel^T  (lower tiles only)
-    OcGemm s{};
-    s.A = panel; s.lda = ld; s.B = panel; s.ldb = ld;
-    s.C = A + (long long)(k0 + nb) * ld + (k0 + nb); s.ldc = ld;
-    s.M = rest; s.N = rest; s.K = nb; s.alpha = -1.f; s.beta = 1.f; s.transA = 0; s.transB = 1;
-    s.flags = OC_GEMM_SKIP_UPPER_TILES; s.batch = 1;
-    rc = oc_gemm_f32_launch(s, stream);
-    if (rc) return rc;
+  // Two levels: inside an outer block of OB columns every 128-column panel updates only the
+  // rest of that outer block (full height); the matrix behind the outer block is updated once per
+  // outer block with K = OB, so it is read and written n/OB times instead of n/128 times.
+  for (int K0 = 0; K0 < n; K0 += OB) {
+    const int kend = min(n, K0 + OB);
+    for (int k0 = K0; k0 < kend; k0 += NB) {
+      const int nb = min(NB, n - k0);
+      potrf_diag_kernel<<<1, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status);
+      OC_CHECK_LAUNCH();
+      const int rest = n - k0 - nb;
+      if (rest <= 0) break;
+      float* panel = A + (long long)(k0 + nb) * ld + k0;
+      OcGemm g{};
+      // panel <- panel * (Lkk^-1)^T  (in place: one column tile, every CTA reads its rows first)
+      g.A = panel; g.lda = ld; g.B = X + (long long)k0 * ld + k0; g.ldb = ld; g.C = panel; g.ldc = ld;
+      g.M = rest; g.N = nb; g.K = nb; g.alpha = 1.f; g.beta = 0.f; g.transA = 0; g.transB = 1;
+      g.flags = 0; g.batch = 1;
+      int rc = oc_gemm_f32_launch(g, stream);
+      if (rc) return rc;
+      const int inner = kend - (k0 + nb);
+      if (inner <= 0) continue;
+      // columns [k0+nb, kend) of all rows below the panel's diagonal block (lower tiles only)
+      OcGemm s{};
+      s.A = panel; s.lda = ld; s.B = panel; s.ldb = ld;
+      s.C = A + (long long)(k0 + nb) * ld + (k0 + nb); s.ldc = ld;
+      s.M = rest; s.N = inner; s.K = nb; s.alpha = -1.f; s.beta = 1.f; s.transA = 0; s.transB = 1;
+      s.flags = OC_GEMM_SKIP_UPPER_TILES; s.batch = 1;
+      rc = oc_gemm_f32_launch(s, stream);
+      if (rc) return rc;
+    }
+    const int rest2 = n - kend;
+    if (rest2 <= 0) break;
+    // trailing <- trailing - P * P^T with P = L[kend.., K0..kend)  (lower tiles only)
+    float* P = A + (long long)kend * ld + K0;
+    OcGemm t{};
+    t.A = P; t.lda = ld; t.B = P; t.ldb = ld;
+    t.C = A + (long long)kend * ld + kend; t.ldc = ld;
+    t.M = rest2; t.N = rest2; t.K = kend - K0; t.alpha = -1.f; t.beta = 1.f; t.transA = 0; t.transB = 1;
+    t.flags = OC_GEMM_SKIP_UPPER_TILES; t.batch = 1;
+    const int rc2 = oc_gemm_f32_launch(t, stream);
+    if (rc2) return rc2;
   }
 
   // ---- recursive blocked inverse of L: X holds the inverted diagonal blocks -----------------

@@ -87,7 +87,8 @@ def test_config5_expert_shapes_group32():
         fac = K.factor_hessian(h, 0.01, False)
         got = K.gptq_quantize(w.to(DEV), fac, wbits=4, groupsize=32, sym=False, want_codes=True)
         ref = orc.gptq_quantize(w, h_ref.clone(), wbits=4, groupsize=32, sym=False)
-        same = (got["codes"].cpu().numpy() == ref["qweight"].numpy()).mean()
+        equal = got["codes"].cpu().numpy() == ref["qweight"].numpy()
+        same = equal.mean()
         if t >= 4 * d:
             assert same >= 0.999, (t, same)
         elif t >= d:
@@ -98,7 +99,13 @@ def test_config5_expert_shapes_group32():
             assert same >= 0.98, (t, same)
         s = got["scales"].cpu().numpy().view(np.uint16).astype(np.int64)
         sref = ref["scales"].numpy().view(np.uint16).astype(np.int64)
-        assert (np.abs(s - sref) <= 1).mean() >= (0.999 if t >= 4 * d else 0.97)
+        close = np.abs(s - sref) <= 1
+        assert close.mean() >= (0.999 if t >= 4 * d else 0.95)
+        # groups fitted before their row's first differing code are untouched by code differences:
+        # there the scales agree to one fp16 ulp whatever the conditioning
+        first_bad = np.where(equal.all(axis=1), d, np.argmin(equal, axis=1))
+        clean = (np.arange(close.shape[0])[:, None] * 32) <= first_bad[None, :]
+        assert close[clean].mean() >= 0.999, (t, close[clean].mean())
 
 
 def test_config4_qwen3_shapes_mixed_bits():
