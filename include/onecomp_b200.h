@@ -34,6 +34,13 @@ extern "C" {
 #define OC_ERR_WORKSPACE (-4)
 #define OC_ERR_TOO_LARGE (-5)
 
+/* 16-bit element type of weights (`w_dtype`) and activations (`x_dtype`).  The reference works on
+ * whatever dtype the model was loaded in (fp16 by default, bf16 for the models that need it,
+ * onecomp/model_config.py:32-63) by casting to fp32; so do these kernels.  Outputs that the
+ * reference leaves in the module's dtype (corrected weight, dequantized weight) use the same type. */
+#define OC_DTYPE_F16 0
+#define OC_DTYPE_BF16 1
+
 int oc_version(void);
 const char* oc_last_error(void);
 /* kernels launched by this library in the calling process so far; reset returns the old count */
@@ -63,7 +70,7 @@ long long oc_launch_count_reset(void);
  */
 int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok, int d,
                     long long ld, float* H, float* C, long long ldh, float a_old, float a_new,
-                    int chunk_tokens, int sm_count, int engine, int* status, void* stream);
+                    int chunk_tokens, int sm_count, int engine, int x_dtype, int* status, void* stream);
 
 /* Same computation as oc_moment_accum for callers that cannot allocate device memory (no
  * counterpart in the reference, which allocates freely through torch).  A host that runs
@@ -85,7 +92,7 @@ int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long lo
 long long oc_moment_static_capacity(void);
 int oc_moment_accum_static(const void* xq, const void* xf, long long n_tok, int d, long long ld,
                            float* H, float* C, long long ldh, float a_old, float a_new,
-                           int chunk_tokens, int sm_count, int* status, void* stream);
+                           int chunk_tokens, int sm_count, int x_dtype, int* status, void* stream);
 
 /* lower triangle <- upper triangle */
 int oc_mirror_upper(float* M, long long ld, int n, void* stream);
@@ -140,8 +147,8 @@ int oc_gptq_quantize(const void* W, long long ldw, int out, int d, const float* 
                      int groupsize, int sym, int blocksize, int mse, int q_grid, float q_norm,
                      int sm_count, int* qweight, int* qzeros,
                      void* scales16, float* scales32, int* zeros, long long ld_out, int* codes,
-                     void* w_hat, long long ldwh, void* workspace, long long workspace_bytes,
-                     void* stream);
+                     void* w_hat, long long ldwh, int w_dtype, void* workspace,
+                     long long workspace_bytes, void* stream);
 
 /* ---- round-to-nearest fallback -----------------------------------------------------
  * Group-wise RTN of W [out, d] fp16 for MoE experts that saw no calibration token
@@ -151,7 +158,7 @@ int oc_gptq_quantize(const void* W, long long ldw, int out, int d, const float* 
  * multiple of the group size.  Outputs: scales, zeros fp32 [out, G]; codes int32 [out, d];
  * deq fp16 [out, d] = fp16((code - zero) * scale). */
 int oc_rtn_quantize(const void* W, long long ldw, int out, int d, int wbits, int groupsize, int sym,
-                    float* scales, float* zeros, int* codes, void* deq, void* stream);
+                    float* scales, float* zeros, int* codes, void* deq, int w_dtype, void* stream);
 
 /* ---- QEP weight correction ------------------------------------------------------
  * W <- fp16( Wz + perccorr * (Wz C) (P^T U^T U P) ), Wz = W with dead columns zeroed,
@@ -162,7 +169,7 @@ int oc_rtn_quantize(const void* W, long long ldw, int out, int d, int wbits, int
 long long oc_qep_workspace_bytes(int out, int d);
 int oc_qep_adjust(void* W, long long ldw, int out, int d, const float* C, long long ldc,
                   const float* U, long long ldu, const int* perm, const unsigned char* dead,
-                  float perccorr, void* workspace, long long workspace_bytes, void* stream);
+                  float perccorr, int w_dtype, void* workspace, long long workspace_bytes, void* stream);
 
 /* ---- block passes of the QEP driver ----------------------------------------------------
  * y = weight * fp16( float(x) * rsqrt(mean(float(x)^2) + eps) ) for x, y [rows, d] fp16 and

@@ -19,18 +19,18 @@ SIGNATURES = {
     "oc_last_error": (c_char_p, []),
     "oc_launch_count": (_L, []),
     "oc_launch_count_reset": (_L, []),
-    "oc_moment_accum": (_I, [_P, _P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _I, _P, _P]),
+    "oc_moment_accum": (_I, [_P, _P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _I, _I, _P, _P]),
     "oc_moment_static_capacity": (_L, []),
-    "oc_moment_accum_static": (_I, [_P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _P, _P]),
+    "oc_moment_accum_static": (_I, [_P, _P, _L, _I, _L, _P, _P, _L, _F, _F, _I, _I, _I, _P, _P]),
     "oc_mirror_upper": (_I, [_P, _L, _I, _P]),
     "oc_hinv_workspace_bytes": (_L, [_I]),
     "oc_hinv_factor": (_I, [_P, _L, _I, _F, _F, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P]),
     "oc_gptq_workspace_bytes": (_L, [_I, _I, _I]),
     "oc_gptq_quantize": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P,
-                              _P, _P, _P, _L, _P, _P, _L, _P, _L, _P]),
-    "oc_rtn_quantize": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+                              _P, _P, _P, _L, _P, _P, _L, _I, _P, _L, _P]),
+    "oc_rtn_quantize": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "oc_qep_workspace_bytes": (_L, [_I, _I]),
-    "oc_qep_adjust": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _F, _P, _L, _P]),
+    "oc_qep_adjust": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _F, _I, _P, _L, _P]),
     "oc_rmsnorm_f16": (_I, [_P, _L, _P, _F, _L, _I, _P, _L, _P]),
     "oc_rope_f16": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P]),
     "oc_swiglu_f16": (_I, [_P, _P, _P, _L, _I, _P]),

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
+#include <cuda_bf16.h>
 #include <stdint.h>
 
 // Status codes returned by every extern "C" entry point.
@@ -41,6 +42,18 @@
 
 void oc_set_last_error(const char* msg);
 void oc_count_launches(int n);
+
+// 16-bit element types of weights and activations (the `dtype` arguments of the C ABI)
+enum : int { OC_DTYPE_F16 = 0, OC_DTYPE_BF16 = 1 };
+
+__device__ __forceinline__ float oc_ld16(const void* p, long long i, int bf16) {
+  return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i])
+              : __half2float(static_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void oc_st16(void* p, long long i, float v, int bf16) {
+  if (bf16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
 
 static inline int oc_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 

@@ -191,18 +191,18 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
 // ---- preparation: fp16 -> fp32, act-order gather, dead columns, per-channel parameters ----
 // Wf[r][j] = dead[perm[j]] ? 0 : float(W[r][perm[j]]).  Per-channel scale / zero are fitted on
 // the whole original row before dead columns are zeroed (reference :690-695).
-__global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_in, int out, int d,
+__global__ void gptq_prepare_kernel(const void* __restrict__ W, int bf16, long long ldw_in, int out, int d,
                                     const int* __restrict__ perm, const unsigned char* __restrict__ dead,
                                     float* __restrict__ Wf, long long ldw, int per_channel, int maxq,
                                     int sym, int mse_steps, float mse_grid, float mse_norm,
                                     float* __restrict__ scales, float* __restrict__ zeros) {
   const int row = blockIdx.x;
-  const __half* src = W + (long long)row * ldw_in;
+  const long long src0 = (long long)row * ldw_in;
   float* dst = Wf + (long long)row * ldw;
   float mn = 0.f, mx = 0.f;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     const int pj = perm ? perm[j] : j;
-    const float v = __half2float(src[pj]);
+    const float v = oc_ld16(W, src0 + pj, bf16);
     mn = fminf(mn, v); mx = fmaxf(mx, v);
     dst[j] = (dead && dead[pj]) ? 0.f : v;
   }
@@ -232,7 +232,7 @@ __global__ void gptq_prepare_kernel(const __half* __restrict__ W, long long ldw_
       mse_candidate(i, mse_grid, rmn, rmx, maxq, sym, zsym, s1, z1);
       float err = 0.f;
       for (int j = threadIdx.x; j < d; j += blockDim.x)
-        err += mse_term(__half2float(src[j]), s1, z1, (float)maxq, mse_norm);
+        err += mse_term(oc_ld16(W, src0 + j, bf16), s1, z1, (float)maxq, mse_norm);
       for (int o = 16; o > 0; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
       __syncthreads();
       if ((threadIdx.x & 31) == 0) smn[threadIdx.x >> 5] = err;
@@ -336,7 +336,7 @@ __global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ code
                                          const int* __restrict__ invperm, int gs,
                                          const float* __restrict__ scales, const float* __restrict__ zeros,
                                          int* __restrict__ codes, long long ldc,
-                                         __half* __restrict__ what, long long ldwh) {
+                                         void* __restrict__ what, long long ldwh, int bf16) {
   __shared__ unsigned short tq[32][33];
   __shared__ float tv[32][33];
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
@@ -357,7 +357,12 @@ __global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ code
     const int r = r0 + k, c = c0 + tx;
     if (c < d && r < out) {
       if (codes) codes[(long long)r * ldc + c] = (int)tq[tx][k];
-      if (what) what[(long long)r * ldwh + c] = __float2half_rn(tv[tx][k]);
+      if (what) {
+        // the reference rounds to fp16 first and casts to the module's dtype afterwards
+        const __half h = __float2half_rn(tv[tx][k]);
+        if (bf16) static_cast<__nv_bfloat16*>(what)[(long long)r * ldwh + c] = __float2bfloat16_rn(__half2float(h));
+        else static_cast<__half*>(what)[(long long)r * ldwh + c] = h;
+      }
     }
   }
 }
@@ -396,12 +401,14 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
                                 int blocksize, int mse, int q_grid, float q_norm, int sm_count,
                                 int* qweight, int* qzeros, void* scales16_,
                                 float* scales32, int* zeros_i32, long long ld_out, int* codes,
-                                void* what_, long long ldwh, void* workspace,
+                                void* what_, long long ldwh, int w_dtype, void* workspace,
                                 long long workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  const __half* W = (const __half*)W_;
+  const void* W = W_;
   __half* scales16 = (__half*)scales16_;
-  __half* what = (__half*)what_;
+  void* what = what_;
+  OC_REQUIRE(w_dtype == OC_DTYPE_F16 || w_dtype == OC_DTYPE_BF16, "gptq_quantize: unknown weight dtype");
+  const int bf16 = w_dtype == OC_DTYPE_BF16;
   OC_REQUIRE(W && U && workspace, "gptq_quantize: null pointer");
   OC_REQUIRE(out > 0 && d > 0 && ldw_in >= d && ldu >= d, "gptq_quantize: bad dimensions");
   OC_REQUIRE(wbits >= 1 && wbits <= 15, "gptq_quantize: wbits must be in 1..15");
@@ -433,7 +440,7 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
 
   OC_REQUIRE(!mse || (q_grid >= 1 && q_norm > 0.f), "gptq_quantize: mse needs q_grid >= 1 and q_norm > 0");
   const int mse_steps = mse ? (int)(0.8 * q_grid) : 0;   // maxshrink = 0.8 as in the reference
-  gptq_prepare_kernel<<<out, 256, 0, stream>>>(W, ldw_in, out, d, perm, dead, Wf, ldw,
+  gptq_prepare_kernel<<<out, 256, 0, stream>>>(W, bf16, ldw_in, out, d, perm, dead, Wf, ldw,
                                                groupsize == -1 ? 1 : 0, maxq, sym, mse_steps,
                                                (float)q_grid, q_norm, scales, zeros);
   OC_CHECK_LAUNCH();
@@ -498,7 +505,7 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
   }
   if (codes || what) {
     unpermute_outputs_kernel<<<dim3(oc_div_up(d, 32), oc_div_up(out, 32)), dim3(32, 8), 0, stream>>>(
-        codesT, out, d, invperm, groupsize, scales, zeros, codes, d, what, ldwh);
+        codesT, out, d, invperm, groupsize, scales, zeros, codes, d, what, ldwh, bf16);
     OC_CHECK_LAUNCH();
   }
   return OC_OK;

@@ -17,8 +17,8 @@ static __device__ __align__(256) __half g_static_delta_scratch[OC_STATIC_SCRATCH
 
 extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok,
                                int d, long long ld, float* H, float* C, long long ldh, float a_old,
-                               float a_new, int chunk_tokens, int sm_count, int force_simt,
-                               int* status, void* stream_);
+                               float a_new, int chunk_tokens, int sm_count, int engine,
+                               int x_dtype, int* status, void* stream_);
 
 namespace {
 constexpr int MAX_DEVICES = 64;
@@ -30,8 +30,8 @@ extern "C" long long oc_moment_static_capacity(void) { return OC_STATIC_SCRATCH_
 // See include/onecomp_b200.h for the contract.
 extern "C" int oc_moment_accum_static(const void* xq, const void* xf, long long n_tok, int d,
                                       long long ld, float* H, float* C, long long ldh, float a_old,
-                                      float a_new, int chunk_tokens, int sm_count, int* status,
-                                      void* stream) {
+                                      float a_new, int chunk_tokens, int sm_count, int x_dtype,
+                                      int* status, void* stream) {
   OC_REQUIRE(n_tok >= 0 && ld >= 0, "moment_accum_static: negative size");
   if (C != nullptr && n_tok * ld > OC_STATIC_SCRATCH_HALFS) {
     oc_set_last_error(
@@ -50,5 +50,5 @@ extern "C" int oc_moment_accum_static(const void* xq, const void* xf, long long 
     g_scratch_addr[dev] = p;
   }
   return oc_moment_accum(xq, xf, g_scratch_addr[dev], n_tok, d, ld, H, C, ldh, a_old, a_new,
-                         chunk_tokens, sm_count, 0, status, stream);
+                         chunk_tokens, sm_count, 0, x_dtype, status, stream);
 }

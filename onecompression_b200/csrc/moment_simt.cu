@@ -26,8 +26,8 @@ __global__ void scale_matrix_kernel(float* __restrict__ M, long long ld, int n, 
 
 // One CTA: 64x64 tile of the d x d moment over a slice of the tokens; adds a_new * partial
 // atomically (the matrix was rescaled by a_old beforehand).
-__global__ void __launch_bounds__(256) moment_simt_kernel(const __half* __restrict__ xq,
-                                                          const __half* __restrict__ xf,
+__global__ void __launch_bounds__(256) moment_simt_kernel(const void* __restrict__ xq,
+                                                          const void* __restrict__ xf, int bf16,
                                                           long long n_tok, int d, long long ld,
                                                           float* __restrict__ H, float* __restrict__ C,
                                                           long long ldh, float a_new, int tok_per_split) {
@@ -46,10 +46,10 @@ __global__ void __launch_bounds__(256) moment_simt_kernel(const __half* __restri
       const long long t = t0 + k;
       float bq = 0.f, aq = 0.f, ad = 0.f;
       if (t < t_end) {
-        if (n0 + c < d) bq = __half2float(xq[t * ld + n0 + c]);
+        if (n0 + c < d) bq = oc_ld16(xq, t * ld + n0 + c, bf16);
         if (m0 + c < d) {
-          aq = __half2float(xq[t * ld + m0 + c]);
-          if (cross) ad = __half2float(xf[t * ld + m0 + c]) - aq;
+          aq = oc_ld16(xq, t * ld + m0 + c, bf16);
+          if (cross) ad = oc_ld16(xf, t * ld + m0 + c, bf16) - aq;
         }
       }
       Bq[k][c] = bq; Aq[k][c] = aq; Ad[k][c] = ad;
@@ -82,8 +82,9 @@ __global__ void __launch_bounds__(256) moment_simt_kernel(const __half* __restri
     }
 }
 
-// delta = fp16( float(xf) - float(xq) ); exact whenever the two values are within a factor
-// of two of each other, which is the rule for a quantisation perturbation.
+// delta = round16( float(xf) - float(xq) ) in the activations' own 16-bit type; exact whenever
+// the two values are within a factor of two of each other, which is the rule for a quantisation
+// perturbation.
 __global__ void delta_f16_kernel(const __half2* __restrict__ xf, const __half2* __restrict__ xq,
                                  __half2* __restrict__ out, long long n2) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -91,6 +92,14 @@ __global__ void delta_f16_kernel(const __half2* __restrict__ xf, const __half2* 
   const float2 f = __half22float2(xf[i]);
   const float2 q = __half22float2(xq[i]);
   out[i] = __floats2half2_rn(f.x - q.x, f.y - q.y);
+}
+__global__ void delta_bf16_kernel(const __nv_bfloat162* __restrict__ xf, const __nv_bfloat162* __restrict__ xq,
+                                  __nv_bfloat162* __restrict__ out, long long n2) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n2) return;
+  const float2 f = __bfloat1622float2(xf[i]);
+  const float2 q = __bfloat1622float2(xq[i]);
+  out[i] = __floats2bfloat162_rn(f.x - q.x, f.y - q.y);
 }
 
 // lower <- upper (mirror across the diagonal), 32x32 tiles
@@ -112,7 +121,7 @@ __global__ void mirror_upper_kernel(float* __restrict__ M, long long ld, int n) 
 
 }  // namespace
 
-int oc_moment_simt_launch(const __half* xq, const __half* xf, long long n_tok, int d, long long ld,
+int oc_moment_simt_launch(const void* xq, const void* xf, int bf16, long long n_tok, int d, long long ld,
                           float* H, float* C, long long ldh, float a_old, float a_new,
                           cudaStream_t stream) {
   const int tb = 256;
@@ -131,17 +140,21 @@ int oc_moment_simt_launch(const __half* xq, const __half* xf, long long n_tok, i
   per = (per + KT - 1) / KT * KT;
   splits = (n_tok + per - 1) / per;
   moment_simt_kernel<<<dim3(tiles, tiles, (unsigned)splits), 256, 0, stream>>>(
-      xq, xf, n_tok, d, ld, H, C, ldh, a_new, (int)per);
+      xq, xf, bf16, n_tok, d, ld, H, C, ldh, a_new, (int)per);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }
 
-int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, cudaStream_t stream) {
+int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, int bf16, cudaStream_t stream) {
   OC_REQUIRE(xf && xq && out && n >= 0 && n % 2 == 0, "delta_f16: null pointer or odd length");
   if (n == 0) return OC_OK;
   const long long n2 = n / 2;
-  delta_f16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, stream>>>(
-      (const __half2*)xf, (const __half2*)xq, (__half2*)out, n2);
+  if (bf16)
+    delta_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat162*)xf, (const __nv_bfloat162*)xq, (__nv_bfloat162*)out, n2);
+  else
+    delta_f16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, stream>>>(
+        (const __half2*)xf, (const __half2*)xq, (__half2*)out, n2);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }

@@ -47,6 +47,7 @@ struct MomentParams {
   float a_old, a_new;
   int chunk_stages;   // stages (of BK tokens) per TMEM accumulation chunk
   int h_tiles, c_tiles, tiles_n;
+  uint32_t idesc;     // IDESC, plus the bf16 operand-format bits for bf16 activations
   int* status;
 };
 
@@ -61,11 +62,11 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
   return d;
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
       "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 // work item -> (matrix, first row, first column)
 __device__ __forceinline__ void decode_item(const MomentParams& p, int item, int& is_c, int& m0, int& n0) {
@@ -167,7 +168,7 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
               // 16 tokens = two 8-token groups = 2048 bytes further into every atom
-              umma_f16(tmem_d, make_desc(sa + kk * 2048), make_desc(sb + kk * 2048),
+              umma_f16(tmem_d, make_desc(sa + kk * 2048), make_desc(sb + kk * 2048), p.idesc,
                        (s > s_begin || kk > 0) ? 1u : 0u);
             }
             umma_commit(smem_u32(&bar_empty[stage]));
@@ -240,14 +241,14 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
   }
 }
 
-int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long ld) {
+int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long ld, int bf16) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { oc_set_last_error("moment: cuTensorMapEncodeTiled is not available"); return OC_ERR_CUDA; }
   cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)n_tok};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)BK};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { oc_set_last_error("moment: cuTensorMapEncodeTiled failed"); return OC_ERR_CUDA; }
@@ -256,21 +257,23 @@ int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long 
 
 }  // namespace
 
-int oc_moment_simt_launch(const __half* xq, const __half* xf, long long n_tok, int d, long long ld,
+int oc_moment_simt_launch(const void* xq, const void* xf, int bf16, long long n_tok, int d, long long ld,
                           float* H, float* C, long long ldh, float a_old, float a_new, cudaStream_t stream);
 
-int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, cudaStream_t stream);
+int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, int bf16, cudaStream_t stream);
 
 int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delta, float* H, float* C,
                           long long ldh, int d, long long n_tok, float a_old, float a_new, int chunk_tokens,
-                          int sm_count, int* status, cudaStream_t stream);
+                          int sm_count, int bf16, int* status, cudaStream_t stream);
 
 // See include/onecomp_b200.h for the contract.
 extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok,
                                int d, long long ld, float* H, float* C, long long ldh, float a_old,
                                float a_new, int chunk_tokens, int sm_count, int engine,
-                               int* status, void* stream_) {
+                               int x_dtype, int* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
+  OC_REQUIRE(x_dtype == OC_DTYPE_F16 || x_dtype == OC_DTYPE_BF16, "moment_accum: unknown activation dtype");
+  const int bf16 = x_dtype == OC_DTYPE_BF16;
   OC_REQUIRE(xq && (H || C) && d > 0 && n_tok >= 0 && ld >= d && ldh >= d, "moment_accum: bad arguments");
   OC_REQUIRE(!C || xf, "moment_accum: the cross term needs the full-precision activations");
   const bool tc_ok = engine != OC_MOMENT_SIMT && d % 8 == 0 && ld % 8 == 0 && ldh % 4 == 0 && n_tok > 0 && status &&
@@ -278,24 +281,24 @@ extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scrat
                      (!H || ((uintptr_t)H & 15) == 0) && (!C || ((uintptr_t)C & 15) == 0);
   if (!tc_ok) {
     // general shapes: fp32 FMA kernel (forms Xf - Xq itself, in fp32)
-    return oc_moment_simt_launch((const __half*)xq, C ? (const __half*)xf : nullptr, n_tok, d, ld,
+    return oc_moment_simt_launch(xq, C ? xf : nullptr, bf16, n_tok, d, ld,
                                  H, C, ldh, a_old, a_new, stream);
   }
   const void* delta_or_xf = nullptr;
   if (C) {
-    int rcd = oc_delta_f16_launch(xf, xq, delta_scratch, n_tok * ld, stream);
+    int rcd = oc_delta_f16_launch(xf, xq, delta_scratch, n_tok * ld, bf16, stream);
     if (rcd) return rcd;
     delta_or_xf = delta_scratch;
   }
   CUtensorMap map_xq, map_delta;
-  int rc = make_map(&map_xq, xq, n_tok, d, ld);
+  int rc = make_map(&map_xq, xq, n_tok, d, ld, bf16);
   if (rc) return rc;
-  if (C) { rc = make_map(&map_delta, delta_or_xf, n_tok, d, ld); if (rc) return rc; }
+  if (C) { rc = make_map(&map_delta, delta_or_xf, n_tok, d, ld, bf16); if (rc) return rc; }
   else map_delta = map_xq;
 
   if (engine == OC_MOMENT_PAIR || (engine == OC_MOMENT_AUTO && OC_MOMENT_AUTO_USES_PAIRS))
     return oc_moment_pair_launch(map_xq, map_delta, H, C, ldh, d, n_tok, a_old, a_new, chunk_tokens, sm_count,
-                                 status, stream);
+                                 bf16, status, stream);
 
   MomentParams p{};
   p.H = H; p.C = C; p.ldh = ldh; p.d = d; p.n_tok = n_tok; p.a_old = a_old; p.a_new = a_new;
@@ -307,6 +310,7 @@ extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scrat
   if (H) for (int tm = 0; tm < tiles_m; ++tm) h_tiles += max(0, p.tiles_n - (tm >> 1));
   p.h_tiles = h_tiles;
   p.c_tiles = C ? tiles_m * p.tiles_n : 0;
+  p.idesc = IDESC | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
   p.status = status;
 
   static bool attr_set = false;

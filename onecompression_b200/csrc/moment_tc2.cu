@@ -39,6 +39,7 @@ struct PairParams {
   float a_old, a_new;
   int chunk_stages;
   int h_tiles, c_tiles, tiles;   // tiles = tiles per matrix side
+  uint32_t idesc;
   int* status;
 };
 
@@ -51,11 +52,11 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr) {
   return d;
 }
 
-__device__ __forceinline__ void umma_pair_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void umma_pair_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
       "  tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 // commit of all earlier MMAs of this thread; arrives on `bar` in both CTAs of the pair
 __device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
@@ -185,7 +186,7 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
             const uint32_t sb = sa + HALF_ATOMS * ATOM_BYTES;
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk)
-              umma_pair_f16(tmem_d, make_desc(sa + kk * 2048), make_desc(sb + kk * 2048),
+              umma_pair_f16(tmem_d, make_desc(sa + kk * 2048), make_desc(sb + kk * 2048), p.idesc,
                             (s > s_begin || kk > 0) ? 1u : 0u);
             umma_pair_commit(smem_u32(&bar_empty[stage]));
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -263,7 +264,7 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
 // when pairs cannot be scheduled on this device, so that the caller can fall back.
 int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delta, float* H, float* C,
                           long long ldh, int d, long long n_tok, float a_old, float a_new, int chunk_tokens,
-                          int sm_count, int* status, cudaStream_t stream) {
+                          int sm_count, int bf16, int* status, cudaStream_t stream) {
   PairParams p{};
   p.H = H; p.C = C; p.ldh = ldh; p.d = d; p.n_tok = n_tok; p.a_old = a_old; p.a_new = a_new;
   if (chunk_tokens <= 0) chunk_tokens = 512;
@@ -271,6 +272,7 @@ int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delt
   p.tiles = oc_div_up(d, PAIR_M);
   p.h_tiles = H ? p.tiles * (p.tiles + 1) / 2 : 0;
   p.c_tiles = C ? p.tiles * p.tiles : 0;
+  p.idesc = IDESC | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
   p.status = status;
   static bool attr_set = false;
   if (!attr_set) {

@@ -10,13 +10,13 @@
 
 namespace {
 
-__global__ void qep_load_kernel(const __half* __restrict__ W, long long ldw_in, int out, int d,
+__global__ void qep_load_kernel(const void* __restrict__ W, long long ldw_in, int out, int d,
                                 const unsigned char* __restrict__ dead, float* __restrict__ Wf,
-                                long long ldw) {
+                                long long ldw, int bf16) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = blockIdx.y;
   if (c >= d) return;
-  const float v = __half2float(W[(long long)r * ldw_in + c]);
+  const float v = oc_ld16(W, (long long)r * ldw_in + c, bf16);
   Wf[(long long)r * ldw + c] = (dead && dead[c]) ? 0.f : v;
 }
 
@@ -28,16 +28,16 @@ __global__ void gather_cols_kernel(const float* __restrict__ src, long long lds,
   dst[(long long)r * ldd + i] = src[(long long)r * lds + (perm ? perm[i] : i)];
 }
 
-// W[r][perm[i]] = fp16( Wf[r][perm[i]] + perccorr * T[r][i] )
+// W[r][perm[i]] = round16( Wf[r][perm[i]] + perccorr * T[r][i] ) in the weight's own 16-bit type
 __global__ void qep_store_kernel(const float* __restrict__ Wf, long long ldw, const float* __restrict__ T,
                                  long long ldt, int out, int d, const int* __restrict__ perm,
-                                 float perccorr, __half* __restrict__ W, long long ldw_out) {
+                                 float perccorr, void* __restrict__ W, long long ldw_out, int bf16) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = blockIdx.y;
   if (i >= d) return;
   const int c = perm ? perm[i] : i;
   const float v = Wf[(long long)r * ldw + c] + perccorr * T[(long long)r * ldt + i];
-  W[(long long)r * ldw_out + c] = __float2half_rn(v);
+  oc_st16(W, (long long)r * ldw_out + c, v, bf16);
 }
 
 long long round4(long long x) { return (x + 3) / 4 * 4; }
@@ -51,9 +51,11 @@ extern "C" long long oc_qep_workspace_bytes(int out, int d) {
 // See include/onecomp_b200.h for the contract.
 extern "C" int oc_qep_adjust(void* W_, long long ldw_io, int out, int d, const float* C, long long ldc,
                              const float* U, long long ldu, const int* perm, const unsigned char* dead,
-                             float perccorr, void* workspace, long long workspace_bytes, void* stream_) {
+                             float perccorr, int w_dtype, void* workspace, long long workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  __half* W = (__half*)W_;
+  void* W = W_;
+  OC_REQUIRE(w_dtype == OC_DTYPE_F16 || w_dtype == OC_DTYPE_BF16, "qep_adjust: unknown weight dtype");
+  const int bf16 = w_dtype == OC_DTYPE_BF16;
   OC_REQUIRE(W && C && U && workspace && out > 0 && d > 0, "qep_adjust: bad arguments");
   OC_REQUIRE(ldw_io >= d && ldc >= d && ldu >= d, "qep_adjust: bad leading dimension");
   OC_REQUIRE(out <= 65535, "qep_adjust: more than 65535 rows in one call");
@@ -67,7 +69,7 @@ extern "C" int oc_qep_adjust(void* W_, long long ldw_io, int out, int d, const f
   float* B = A + (long long)out * ld;
   const int tb = 256;
   dim3 grid(oc_div_up(d, tb), out);
-  qep_load_kernel<<<grid, tb, 0, stream>>>(W, ldw_io, out, d, dead, Wf, ld);
+  qep_load_kernel<<<grid, tb, 0, stream>>>(W, ldw_io, out, d, dead, Wf, ld, bf16);
   OC_CHECK_LAUNCH();
   OcGemm g{};
   // A = Wf * C
@@ -90,7 +92,7 @@ extern "C" int oc_qep_adjust(void* W_, long long ldw_io, int out, int d, const f
   t2.M = out; t2.N = d; t2.K = d; t2.alpha = 1.f; t2.beta = 0.f; t2.flags = OC_GEMM_KHI_FROM_N; t2.batch = 1;
   rc = oc_gemm_f32_launch(t2, stream);
   if (rc) return rc;
-  qep_store_kernel<<<grid, tb, 0, stream>>>(Wf, ld, B, ld, out, d, perm, perccorr, W, ldw_io);
+  qep_store_kernel<<<grid, tb, 0, stream>>>(Wf, ld, B, ld, out, d, perm, perccorr, W, ldw_io, bf16);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }

@@ -45,6 +45,10 @@ def _require_cuda(t: torch.Tensor, what: str):
 # ---------------------------------------------------------------------------
 
 
+# 16-bit element types the kernels read and write (the C ABI's OC_DTYPE_* codes)
+_DTYPES = {torch.float16: 0, torch.bfloat16: 1}
+
+
 class MomentAccumulator:
     """Running-mean Hessian H = (2/N) XqᵀXq and, optionally, the QEP cross term
     C = (2/N)(Xf − Xq)ᵀXq, accumulated chunk by chunk on the GPU.
@@ -89,6 +93,8 @@ class MomentAccumulator:
             xf = self._as_rows(xf)
             if xf.shape != xq.shape:
                 raise ValueError("xf and xq differ in shape")
+            if xf.dtype != xq.dtype:
+                xf = xf.to(xq.dtype)
         n = self.nsamples
         a_old = n / (n + t)
         a_new = 2.0 / (n + t)
@@ -96,19 +102,19 @@ class MomentAccumulator:
         scratch = None
         if cross and not self.force_simt:
             if self._scratch is None or self._scratch.numel() < xq.numel():
-                self._scratch = torch.empty(xq.numel(), dtype=torch.float16, device=self.device)
+                self._scratch = torch.empty(xq.numel(), dtype=xq.dtype, device=self.device)
             scratch = self._scratch
         with torch.cuda.device(self.device):
             call(
                 "oc_moment_accum", ptr(xq), ptr(xf) if cross else None, ptr(scratch), t, self.d,
                 xq.stride(0), ptr(self.H), ptr(self.C), self.d, a_old, a_new, self.chunk_tokens,
-                sm_count(self.device), self.engine, ptr(self.status), stream_handle(),
+                sm_count(self.device), self.engine, _DTYPES[xq.dtype], ptr(self.status), stream_handle(),
             )
         self._needs_mirror = not self.force_simt
 
     def _as_rows(self, x: torch.Tensor) -> torch.Tensor:
         _require_cuda(x, "activations")
-        if x.dtype != torch.float16:
+        if x.dtype not in _DTYPES:
             x = x.to(torch.float16)
         x = x.reshape(-1, self.d)
         if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
@@ -262,8 +268,8 @@ def gptq_quantize(
     ``ld_out``, the row count of the full layer.
     """
     _require_cuda(weight, "weight")
-    if weight.dtype != torch.float16:
-        raise TypeError("gptq_quantize expects an fp16 weight")
+    if weight.dtype not in _DTYPES:
+        raise TypeError("gptq_quantize expects an fp16 or bf16 weight")
     if weight.dim() != 2:
         raise ValueError("weight must be 2-D [out_features, in_features]")
     if weight.stride(1) != 1:
@@ -303,7 +309,7 @@ def gptq_quantize(
     if want_codes and "codes" not in outputs:
         outputs["codes"] = torch.empty((out, d), dtype=torch.int32, device=dev)
     if want_dequantized and "dequantized" not in outputs:
-        outputs["dequantized"] = torch.empty((out, d), dtype=torch.float16, device=dev)
+        outputs["dequantized"] = torch.empty((out, d), dtype=weight.dtype, device=dev)
     deq = outputs.get("dequantized")
     with torch.cuda.device(dev):
         nbytes = _lib.load().oc_gptq_workspace_bytes(out, d, groupsize)
@@ -316,7 +322,7 @@ def gptq_quantize(
             ptr(outputs.get("qweight")),
             ptr(outputs.get("qzeros")), ptr(outputs["scales"]), ptr(outputs.get("scales_f32")),
             ptr(outputs["zeros"]), ld, ptr(outputs.get("codes")), ptr(deq),
-            deq.stride(0) if deq is not None else d, ptr(ws), ws.numel(), stream_handle(),
+            deq.stride(0) if deq is not None else d, _DTYPES[weight.dtype], ptr(ws), ws.numel(), stream_handle(),
         )
     return outputs
 
@@ -327,10 +333,10 @@ def gptq_quantize(
 
 
 def qep_adjust(weight: torch.Tensor, c: torch.Tensor, factor: HessianFactor, perccorr: float):
-    """In place: weight ← fp16(Wz + perccorr·(Wz·C)·(H+damp·I)⁻¹) for an fp16 CUDA weight."""
+    """In place: weight ← round16(Wz + perccorr·(Wz·C)·(H+damp·I)⁻¹) for an fp16 or bf16 CUDA weight."""
     _require_cuda(weight, "weight")
-    if weight.dtype != torch.float16 or weight.dim() != 2 or weight.stride(1) != 1:
-        raise TypeError("qep_adjust expects a 2-D fp16 weight with contiguous rows")
+    if weight.dtype not in _DTYPES or weight.dim() != 2 or weight.stride(1) != 1:
+        raise TypeError("qep_adjust expects a 2-D fp16 or bf16 weight with contiguous rows")
     if c.dtype != torch.float32 or c.stride(1) != 1:
         c = c.float().contiguous()
     out, d = weight.shape
@@ -344,17 +350,17 @@ def qep_adjust(weight: torch.Tensor, c: torch.Tensor, factor: HessianFactor, per
             call(
                 "oc_qep_adjust", ptr(slab), slab.stride(0), rows, d, ptr(c), c.stride(0),
                 ptr(factor.u), factor.u.stride(0), ptr(factor.perm) if factor.actorder else None,
-                ptr(factor.dead), float(perccorr), ptr(ws), ws.numel(), stream_handle(),
+                ptr(factor.dead), float(perccorr), _DTYPES[weight.dtype], ptr(ws), ws.numel(), stream_handle(),
             )
     return weight
 
 
 def rtn_quantize(weight: torch.Tensor, wbits: int, groupsize: int, sym: bool):
     """Round-to-nearest group quantization (no Hessian).  Returns dict(codes int32 [out,d],
-    scales fp32 [out,G], zeros fp32 [out,G], dequantized fp16 [out,d]) on the device."""
+    scales fp32 [out,G], zeros fp32 [out,G], dequantized [out,d] in the weight's dtype) on the device."""
     _require_cuda(weight, "weight")
-    if weight.dtype != torch.float16 or weight.dim() != 2:
-        raise TypeError("rtn_quantize expects a 2-D fp16 weight")
+    if weight.dtype not in _DTYPES or weight.dim() != 2:
+        raise TypeError("rtn_quantize expects a 2-D fp16 or bf16 weight")
     if weight.stride(1) != 1:
         weight = weight.contiguous()
     out, d = weight.shape
@@ -367,12 +373,12 @@ def rtn_quantize(weight: torch.Tensor, wbits: int, groupsize: int, sym: bool):
         "codes": torch.empty((out, d), dtype=torch.int32, device=dev),
         "scales": torch.empty((out, groups), dtype=torch.float32, device=dev),
         "zeros": torch.empty((out, groups), dtype=torch.float32, device=dev),
-        "dequantized": torch.empty((out, d), dtype=torch.float16, device=dev),
+        "dequantized": torch.empty((out, d), dtype=weight.dtype, device=dev),
     }
     with torch.cuda.device(dev):
         call("oc_rtn_quantize", ptr(weight), weight.stride(0), out, d, wbits, groupsize, 1 if sym else 0,
              ptr(res["scales"]), ptr(res["zeros"]), ptr(res["codes"]), ptr(res["dequantized"]),
-             stream_handle())
+             _DTYPES[weight.dtype], stream_handle())
     return res
 
 

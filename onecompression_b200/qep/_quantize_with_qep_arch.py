@@ -160,7 +160,7 @@ def _rtn_fallback_result(module, quantizer, name):
     wbits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
     groupsize = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
     weight = module.weight.data
-    out = kernels.rtn_quantize(weight if weight.dtype == torch.float16 else weight.half(),
+    out = kernels.rtn_quantize(weight if weight.dtype in (torch.float16, torch.bfloat16) else weight.half(),
                                wbits, groupsize, quantizer.sym)
     scales = out["scales"].to(torch.float16).cpu()
     zeros = out["zeros"].to(torch.float16).cpu()

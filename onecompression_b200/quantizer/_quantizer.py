@@ -192,7 +192,7 @@ class Quantizer(metaclass=ABCMeta):
         )
         if not usable:
             factor = kernels.factor_hessian(hessian, percdamp, actorder=False, shifts=_qep_shift_rule())
-        w16 = weight if weight.dtype == torch.float16 else weight.to(torch.float16)
+        w16 = weight if weight.dtype in (torch.float16, torch.bfloat16) else weight.to(torch.float16)
         w16 = w16.contiguous() if w16.stride(-1) != 1 else w16
         kernels.qep_adjust(w16, delta_hatx, factor, perccorr)
         if w16.data_ptr() != weight.data_ptr():

@@ -200,7 +200,7 @@ class AutoBitQuantizer(Quantizer):
         w = module.weight.data
         if not w.is_cuda:
             raise RuntimeError("AutoBit evaluates its RTN errors on the GPU: move the model to a CUDA device")
-        w16 = w if w.dtype == torch.float16 else w.half()
+        w16 = w if w.dtype in (torch.float16, torch.bfloat16) else w.half()
         a = b = None
         if (self.assignment_strategy == "activation_aware" and self.input_moments is not None
                 and self.output_curvature is not None):

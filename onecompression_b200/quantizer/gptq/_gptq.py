@@ -308,13 +308,14 @@ class GPTQ(Quantizer):
         name = self.module_to_name.get(module)
         w = getattr(module, "weight", None)
         if (name is None or type(module) is not torch.nn.Linear or w is None or not w.is_cuda
-                or w.dtype != torch.float16 or w.shape[0] % 32 != 0 or self.calc_quant_error):
+                or w.dtype not in (torch.float16, torch.bfloat16) or w.shape[0] % 32 != 0
+                or self.calc_quant_error):
             return None
         bits = GPTQ.resolve_bits(name, self.wbits, self.mlp_wbits, self.module_wbits)
         gs = GPTQ.resolve_groupsize(name, self.groupsize, self.mlp_groupsize)
         if self.bitpack_on_quantize and not is_packable_wbits(bits):
             return None
-        return (id(self), bits, gs, w.shape[1], w.device)
+        return (id(self), bits, gs, w.shape[1], w.device, w.dtype)
 
     def quantize_stacked(self, modules, hessian, factor, delta_hatX=None, percdamp=0.01, perccorr=0.5):
         """``quantize_with_qep`` for several layers that share ``hessian`` (equal ``stack_key``):
@@ -476,8 +477,8 @@ def _gptq_device(hessian, layer, blocksize, percdamp, wbits, groupsize, actorder
     w = _weight_matrix(layer)
     if not w.is_cuda:
         raise RuntimeError("GPTQ: the layer must live on a CUDA device (this build has no CPU path)")
-    if w.dtype != torch.float16:
-        raise TypeError(f"GPTQ: fp16 weights expected, got {w.dtype}")
+    if w.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"GPTQ: fp16 or bf16 weights expected, got {w.dtype}")
     if factor is None:
         if hessian is None:
             raise ValueError("GPTQ needs the layer's Hessian")

@@ -35,6 +35,16 @@ def f16(bits):
     return torch.from_numpy(np.ascontiguousarray(bits).view(np.float16).copy())
 
 
+def bf16(bits):
+    """bfloat16 tensor from its raw bits (fixtures store bf16 as uint16)."""
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16).copy()).view(torch.bfloat16)
+
+
+def bits16(t):
+    """Raw bits of an fp16 / bf16 tensor as a uint16 array."""
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
 def gptq_case_names():
     return sorted(
         f[len("gptq_") : -len(".npz")] for f in os.listdir(GOLDEN) if f.startswith("gptq_")

@@ -63,6 +63,8 @@ def _np(t):
         return np.zeros((0,), dtype=np.int64)
     if t.dtype == torch.float16:
         return t.numpy().view(np.uint16)  # stored as raw bits
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)  # raw bits as well
     return t.numpy()
 
 
@@ -243,6 +245,38 @@ def main(ref_root):
         rtn[f"zero_{key}"] = _np(r["zero"])
         rtn[f"deq_{key}"] = _np(r["dequantized_weight"])
     np.savez_compressed(os.path.join(HERE, "rtn.npz"), **rtn)
+
+    # ---- bf16 module: moments, correction, GPTQ, RTN on bfloat16 weights and activations ----------
+    b = {}
+    w, x = synth_layer(500, 32, 256, 1024)
+    g = torch.Generator().manual_seed(501)
+    w, x = w.bfloat16(), x.bfloat16()
+    xq = (x.float() * (1 + 0.05 * torch.randn(x.shape, generator=g))).bfloat16()
+    lin = torch.nn.Linear(256, 32, bias=False).bfloat16()
+    lin.weight.data = w.clone()
+    qz = ref_gptq.GPTQ(wbits=4, groupsize=64, sym=False)
+    qz.module_to_name = {lin: "layer"}
+    h, n = qz.calculate_hessian(lin, xq.unsqueeze(0))
+    c = qz.calculate_delta_hatX(lin, xq.unsqueeze(0), x.unsqueeze(0))
+    raw = ref_gptq.run_gptq(h.clone(), lin, blocksize=128, percdamp=0.01, wbits=4, groupsize=64,
+                            actorder=False, mse=False, sym=False)
+    b.update(W=_np(w), xq=_np(xq), xf=_np(x), H=h.numpy(), C=c.numpy(), n=np.int64(n),
+             codes=raw["qweight"].numpy(), scales=_np(raw["scales"]), qzeros=raw["qzeros"].numpy())
+    qz.adjust_weight(lin, None, None, original_hessian=h, original_delta_hatX=c, percdamp=0.01, perccorr=0.5)
+    b["adjusted"] = _np(lin.weight.data.clone())
+    lin.weight.data = w.clone()
+    qz.quantize_with_qep(lin, None, None, percdamp=0.01, perccorr=0.5, hessian=h.clone(), delta_hatX=c.clone())
+    res = qz.results["layer"]
+    deq = res.compute_dequantized_weight()
+    b.update(qep_qweight_packed=res.qweight.numpy(), qep_qzeros_packed=res.qzeros.numpy(),
+             qep_scales=_np(res.scales), qep_dequantized=_np(deq),
+             qep_installed=_np(deq.to(torch.bfloat16)))      # what the driver puts into the module
+    lin.weight.data = w.clone()
+    r = run_rtn(lin, wbits=4, groupsize=32, sym=False)
+    b.update(rtn_codes=r["quantized_weight"].numpy(), rtn_scale=_np(r["scale"]), rtn_zero=_np(r["zero"]),
+             rtn_deq=_np(r["dequantized_weight"]))
+    b["rtn_deq_is_bf16"] = np.int64(r["dequantized_weight"].dtype == torch.bfloat16)
+    np.savez_compressed(os.path.join(HERE, "bf16.npz"), **b)
     print("golden fixtures written to", HERE)
 
 

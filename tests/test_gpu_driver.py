@@ -125,8 +125,10 @@ class _Recorder:
         return super().quantize_with_qep(module, *a, **kw)
 
 
-@pytest.mark.parametrize("bits,gs,sym,act", [(3, 128, True, False), (4, 64, False, True)])
-def test_block_driver_layers_match_oracle(bits, gs, sym, act):
+@pytest.mark.parametrize("bits,gs,sym,act,dtype", [(3, 128, True, False, torch.float16),
+                                                     (4, 64, False, True, torch.float16),
+                                                     (4, 128, False, False, torch.bfloat16)])
+def test_block_driver_layers_match_oracle(bits, gs, sym, act, dtype):
     from onecompression_b200 import GPTQ, QEPConfig, synthetic
     from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
 
@@ -135,8 +137,8 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act):
 
     shape = dict(synthetic.LLAMA3_8B, hidden_size=256, intermediate_size=512, num_attention_heads=4,
                  num_key_value_heads=2, head_dim=64, vocab_size=1000)
-    stack = synthetic.llama_blocks(shape, 2, 64, DEV, seed=3)
-    x0 = synthetic.embedded_tokens(1000, 256, 48, 64, DEV, seed=3) * 30   # unit-scale activations
+    stack = synthetic.llama_blocks(shape, 2, 64, DEV, seed=3, dtype=dtype)
+    x0 = synthetic.embedded_tokens(1000, 256, 48, 64, DEV, seed=3, dtype=dtype) * 30   # unit-scale activations
     q = Rec(wbits=bits, groupsize=gs, sym=sym, actorder=act)
     q.seen, q.inputs = [], {}
     for i, blk in enumerate(stack.blocks):
@@ -178,7 +180,8 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act):
         assert eq.mean() >= 0.99, f"{name}: {eq.mean():.5f}"
         # the block now holds the dequantised weight
         mod = dict(stack.blocks[i].named_modules())[name.split(".", 3)[3]]
-        assert torch.equal(mod.weight.data.cpu(), r.compute_dequantized_weight())
+        assert mod.weight.dtype == dtype
+        assert torch.equal(mod.weight.data.cpu(), r.compute_dequantized_weight().to(dtype))
     assert total > 0 and matched / total >= 0.999, f"{matched / total:.5f} identical codes over all layers"
 
 

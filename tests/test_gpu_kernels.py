@@ -402,3 +402,51 @@ def test_swiglu_is_bit_identical_to_the_model_code(K, shape):
     assert torch.equal(K.swiglu_f16(gate, up), want)
     g2 = gate.clone()
     assert K.swiglu_f16(g2, up, inplace=True).data_ptr() == g2.data_ptr() and torch.equal(g2, want)
+
+
+# ---- bfloat16 modules --------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("engine", ["single", "pair", "simt"])
+def test_bf16_moments_match_reference_vectors(K, engine):
+    from conftest import bf16
+
+    g = load_golden("bf16.npz")
+    xq, xf = bf16(g["xq"]).to(dev()), bf16(g["xf"]).to(dev())
+    acc = K.MomentAccumulator(256, dev(), cross=True, engine=engine)
+    for a, b in zip(xq.split(8 * 64), xf.split(8 * 64)):     # the reference's slices of 8 "sequences"
+        acc.add(a, b)
+    h, c, n = acc.finalize()
+    assert n == int(g["n"])
+    assert _rel(h.cpu(), torch.from_numpy(g["H"])) < 1e-5
+    assert _rel(c.cpu(), torch.from_numpy(g["C"])) < 1e-4
+
+
+def test_bf16_layer_matches_reference_vectors(K):
+    """GPTQ, QEP correction (written back in bf16), installed weight and RTN on a bf16 module."""
+    from conftest import bf16, bits16
+
+    g = load_golden("bf16.npz")
+    w = bf16(g["W"]).to(dev())
+    h, c = torch.from_numpy(g["H"]).to(dev()), torch.from_numpy(g["C"]).to(dev())
+    fac = K.factor_hessian(h, 0.01, False)
+    got = K.gptq_quantize(w, fac, wbits=4, groupsize=64, sym=False, want_codes=True)
+    assert (got["codes"].cpu().numpy() == g["codes"]).mean() >= 0.999
+    assert np.abs(bits16(got["scales"]).astype(np.int64) - g["scales"].astype(np.int64)).max() <= 1
+    adj = w.clone()
+    K.qep_adjust(adj, c, fac, 0.5)
+    assert adj.dtype == torch.bfloat16
+    d_adj = np.abs(bits16(adj).astype(np.int64) - g["adjusted"].astype(np.int64))
+    assert d_adj.max() <= 1 and (d_adj == 0).mean() > 0.99
+    # from the reference's own corrected weight, the packed result and the weight the driver installs
+    from conftest import bf16 as _b
+
+    adj_ref = _b(g["adjusted"]).to(dev())
+    q2 = K.gptq_quantize(adj_ref, fac, wbits=4, groupsize=64, sym=False, want_codes=True)
+    same = q2["qweight"].cpu().numpy() == g["qep_qweight_packed"]
+    assert same.mean() >= 0.995
+    if same.all() and np.array_equal(bits16(q2["scales"]), g["qep_scales"]):
+        assert q2["dequantized"].dtype == torch.bfloat16
+        assert np.array_equal(bits16(q2["dequantized"]), g["qep_installed"])
+    rt = K.rtn_quantize(w, 4, 32, False)
+    assert np.array_equal(rt["codes"].cpu().numpy(), g["rtn_codes"])
+    assert rt["dequantized"].dtype == torch.bfloat16 and np.array_equal(bits16(rt["dequantized"]), g["rtn_deq"])

@@ -142,3 +142,33 @@ def test_rtn_matches_reference(bits, gs, sym):
     assert np.array_equal(r["dequantized_weight"].numpy().view(np.uint16), g[f"deq_{key}"])
     with pytest.raises(ValueError):
         orc.rtn_quantize(f16(g["W"]), 4, 48, False)
+
+
+def test_bf16_module_matches_reference():
+    """bfloat16 weights and activations: moments, correction written back in bf16, GPTQ and RTN."""
+    from conftest import bf16, bits16
+
+    torch.set_num_threads(1)
+    g = load_golden("bf16.npz")
+    w, xq, xf = bf16(g["W"]), bf16(g["xq"]), bf16(g["xf"])
+    h, n = orc.hessian_running_mean(xq.unsqueeze(0))
+    assert n == int(g["n"]) and np.array_equal(h.numpy(), g["H"])
+    c = orc.delta_hatx_running_mean(xq.unsqueeze(0), xf.unsqueeze(0))
+    assert np.array_equal(c.numpy(), g["C"])
+    r = orc.gptq_quantize(w, h.clone(), wbits=4, groupsize=64, sym=False)
+    assert np.array_equal(r["qweight"].numpy(), g["codes"])
+    assert np.array_equal(r["scales"].numpy().view(np.uint16), g["scales"])
+    assert np.array_equal(r["qzeros"].numpy(), g["qzeros"])
+    adj = orc.qep_adjust_weight(w, h, c, 0.01, 0.5)
+    assert adj.dtype == torch.bfloat16 and np.array_equal(bits16(adj), g["adjusted"])
+    r2 = orc.gptq_quantize(adj, h.clone(), wbits=4, groupsize=64, sym=False)
+    qw, qz = orc.pack_result(r2["qweight"].numpy(), r2["qzeros"].numpy(), 4)
+    assert np.array_equal(qw, g["qep_qweight_packed"]) and np.array_equal(qz, g["qep_qzeros_packed"])
+    assert np.array_equal(r2["scales"].numpy().view(np.uint16), g["qep_scales"])
+    deq = orc.dequantize_result(qw, r2["scales"], qz, None, 4, 64, (32, 256))
+    assert np.array_equal(bits16(deq), g["qep_dequantized"])
+    assert np.array_equal(bits16(deq.to(torch.bfloat16)), g["qep_installed"])
+    rt = orc.rtn_quantize(w, 4, 32, False)
+    assert np.array_equal(rt["quantized_weight"].numpy(), g["rtn_codes"])
+    assert rt["dequantized_weight"].dtype == torch.bfloat16 and int(g["rtn_deq_is_bf16"]) == 1
+    assert np.array_equal(bits16(rt["dequantized_weight"]), g["rtn_deq"])

@@ -23,10 +23,10 @@ def _accumulate(lib, name, xq, xf, h, c, n_before, status, scratch=None):
     a_old, a_new = n_before / (n_before + t), 2.0 / (n_before + t)
     if name == "oc_moment_accum":
         rc = lib.oc_moment_accum(ptr(xq), ptr(xf), ptr(scratch), t, d, xq.stride(0), ptr(h), ptr(c), d,
-                                 a_old, a_new, 0, 0, 0, ptr(status), stream_handle())
+                                 a_old, a_new, 0, 0, 0, 0, ptr(status), stream_handle())
     else:
         rc = lib.oc_moment_accum_static(ptr(xq), ptr(xf), t, d, xq.stride(0), ptr(h), ptr(c), d,
-                                        a_old, a_new, 0, 0, ptr(status), stream_handle())
+                                        a_old, a_new, 0, 0, 0, ptr(status), stream_handle())
     return rc
 
 
