@@ -669,7 +669,7 @@ class BlockQuantizer:
                     factor = factors[key]
                 excluded = self._excluded(name)
                 skey = None
-                if child is not None and self.stack_layers and self.dist is None:
+                if child is not None and self.stack_layers and (self.dist is None or child.bitpack_on_quantize):
                     skey = child.stack_key(module)
                     if skey is not None:
                         skey = skey + (excluded,)
@@ -683,8 +683,15 @@ class BlockQuantizer:
             for entry in plan:
                 mods, excluded = entry["modules"], entry["excluded"]
                 if len(mods) > 1:
-                    results = entry["child"].quantize_stacked(
-                        mods, h, entry["factor"], None if excluded else c, self.cfg.percdamp, self.cfg.perccorr)
+                    if self.dist is not None:
+                        results = self.dist.quantize_rows_stacked(
+                            entry["child"], mods, h, None if excluded else c, self.cfg, entry["factor"])
+                        for module in mods:
+                            entry["child"].results.pop(qz.module_to_name[module], None)
+                    else:
+                        results = entry["child"].quantize_stacked(
+                            mods, h, entry["factor"], None if excluded else c, self.cfg.percdamp,
+                            self.cfg.perccorr)
                     for module in mods:
                         name = qz.module_to_name[module]
                         qz.results[name] = results[module]

@@ -89,16 +89,25 @@ class ShardedContext:
         ``compute(weight_slab, c) -> dict`` produces the slab's outputs (qweight
         [in·bits/32, rows], qzeros [G, rows·bits/32], scales [G, rows], zeros [G, rows],
         dequantized [rows, in]); the default runs the CUDA kernels."""
+        return self.quantize_rows_stacked(quantizer, [module], h, c, cfg, factor, compute)[module]
+
+    def quantize_rows_stacked(self, quantizer, modules, h, c, cfg, factor,
+                              compute: Optional[Callable] = None):
+        """``quantize_rows`` for several layers that share the Hessian and the settings: their
+        weights are stacked row-wise, the stacked rows are split over the ranks, and the gathered
+        result is cut back into one GPTQResult per layer (rows never interact, so the results are
+        those of the per-layer calls).  Returns {module: GPTQResult}."""
         import time
 
         from . import kernels
         from .quantizer.gptq._gptq import GPTQ, GPTQResult
 
-        name = quantizer.module_to_name[module]
+        names = [quantizer.module_to_name[m] for m in modules]
         t0 = time.time()
-        bits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
-        gs = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
-        weight = module.weight.data
+        bits = GPTQ.resolve_bits(names[0], quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
+        gs = GPTQ.resolve_groupsize(names[0], quantizer.groupsize, quantizer.mlp_groupsize)
+        rows = [m.weight.shape[0] for m in modules]
+        weight = modules[0].weight.data if len(modules) == 1 else torch.cat([m.weight.data for m in modules], 0)
         out_features, d = weight.shape
         first, last = row_slab(out_features, self.rank, self.world)
         slab = weight[first:last]
@@ -113,7 +122,7 @@ class ShardedContext:
                         "qzeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
                         "scales": torch.empty((groups, 0), dtype=torch.float16, device=dev),
                         "zeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
-                        "dequantized": torch.empty((0, d), dtype=torch.float16, device=dev),
+                        "dequantized": torch.empty((0, d), dtype=w_slab.dtype, device=dev),
                     }
                 if cross is not None:
                     kernels.qep_adjust(w_slab, cross, factor, cfg.perccorr)
@@ -126,20 +135,30 @@ class ShardedContext:
         scales = self.gather_rows(local["scales"], out_features, dim=1)
         w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
         perm = getattr(factor, "perm", None) if quantizer.actorder else None
+        pieces, r0 = [], 0
+        for r in rows:
+            pieces += [qweight[:, r0:r0 + r], scales[:, r0:r0 + r], qzeros[:, r0 * bits // 32:(r0 + r) * bits // 32]]
+            r0 += r
+        perm64 = perm.to(torch.int64) if perm is not None else None
         if qweight.is_cuda:
-            qweight, scales, qzeros, perm = kernels.to_host(
-                [qweight, scales, qzeros, perm.to(torch.int64) if perm is not None else None])
-        elif perm is not None:
-            perm = perm.to(torch.int64)
-        result = GPTQResult(
-            wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
-            qweight=qweight, scales=(scales if gs != -1 else scales.reshape(out_features, 1)),
-            qzeros=qzeros, perm=perm,
-            qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(out_features, d),
-        )
-        result.__dict__["_device_dequantized"] = w_hat
+            host = kernels.to_host(pieces + [perm64])
+        else:
+            host = [p.contiguous() for p in pieces] + [perm64]
         if weight.is_cuda:
             torch.cuda.synchronize(weight.device)
-        result.quantization_time = time.time() - t0
-        quantizer.results[name] = result
-        return result
+        elapsed = time.time() - t0
+        results, r0 = {}, 0
+        for i, (m, name, r) in enumerate(zip(modules, names, rows)):
+            qw, sc, qz = host[3 * i], host[3 * i + 1], host[3 * i + 2]
+            result = GPTQResult(
+                wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
+                qweight=qw, scales=(sc if gs != -1 else sc.reshape(r, 1)), qzeros=qz,
+                perm=host[-1].clone() if host[-1] is not None else None,
+                qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(r, d),
+            )
+            result.__dict__["_device_dequantized"] = w_hat[r0:r0 + r]
+            result.quantization_time = elapsed * r / out_features
+            quantizer.results[name] = result
+            results[m] = result
+            r0 += r
+        return results

@@ -87,6 +87,23 @@ def _worker(rank, world, port, out_dir):
     assert torch.equal(res.scales, whole["scales"])
     assert torch.equal(res.__dict__["_device_dequantized"], whole["dequantized"])
     assert q.results["layer"] is res
+
+    # two layers with one input, stacked: the stacked rows are split over the ranks and the gathered
+    # result is cut back per layer; slabs may straddle the boundary between the layers
+    w2 = (torch.randn(64, d, generator=g) * 0.02).half()
+    lin_a, lin_b = torch.nn.Linear(d, out, bias=False).half(), torch.nn.Linear(d, 64, bias=False).half()
+    lin_a.weight.data, lin_b.weight.data = w.clone(), w2.clone()
+    q2 = GPTQ(wbits=4, groupsize=32, sym=False)
+    q2.module_to_name = {lin_a: "a", lin_b: "b"}
+    both = ctx.quantize_rows_stacked(q2, [lin_a, lin_b], h_all, c_all, QEPConfig(), F(), compute=compute)
+    for lin_x, w_x, key in ((lin_a, w, "a"), (lin_b, w2, "b")):
+        alone = compute(w_x, c_all)
+        r = both[lin_x]
+        assert q2.results[key] is r and r.qweight_original_shape == (w_x.shape[0], d)
+        assert np.array_equal(r.qweight.numpy(), alone["qweight"].numpy())
+        assert np.array_equal(r.qzeros.numpy(), alone["qzeros"].numpy())
+        assert torch.equal(r.scales, alone["scales"])
+        assert torch.equal(r.__dict__["_device_dequantized"], alone["dequantized"])
     open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     dist.destroy_process_group()
 

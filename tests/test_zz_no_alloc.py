@@ -84,7 +84,7 @@ def test_static_scratch_rejects_oversized_call():
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     # claim more tokens than the scratch holds: refused before anything is launched
     rc = lib.oc_moment_accum_static(x.data_ptr(), x.data_ptr(), cap // d + 1, d, d, h.data_ptr(),
-                                    c.data_ptr(), d, 0.0, 1.0, 0, 0, status.data_ptr(),
+                                    c.data_ptr(), d, 0.0, 1.0, 0, 0, 0, status.data_ptr(),
                                     torch.cuda.current_stream().cuda_stream)
     assert rc == -5
     assert b"built-in scratch" in lib.oc_last_error()
