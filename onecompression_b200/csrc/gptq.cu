@@ -92,7 +92,10 @@ __device__ __noinline__ void fit_group(const float* __restrict__ src, int n, int
 // tiles is not left to a single warp when a CTA owns few rows.
 constexpr int LOADERS = 256;
 
-template <int WARPS>
+// ALIGNED: every group starts on a multiple of SUB columns (per-channel, or a group size that is
+// a multiple of SUB), so the fit can only fall on the first column of a register window and the
+// other fifteen unrolled column steps carry no test and no call site for it.
+template <int WARPS, bool ALIGNED>
 __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
   extern __shared__ __align__(16) float sm[];
   float* Us = sm;               // [BLK][BLK], upper triangle of the diagonal block of U
@@ -118,6 +121,8 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
   const float* grow = a.Wf + (long long)row * a.ldw;  // block-entry state of the whole row
   const float maxqf = (float)a.maxq;
   const int gs = a.gs;
+  unsigned short* code_out = a.codesT + (long long)i1 * a.out + row;   // + column * out
+  float* err_out = a.ErrT + row;                                        // + column * lde
   float scale, zero;
   if (gs == -1) { scale = a.scales[row]; zero = a.zeros[row]; }
   else if (i1 % gs != 0) {
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
       er[i] = 0.f;
       if (ci < count) {
         const int col = i1 + ci;
-        if (gs != -1 && col % gs == 0) {
+        if ((!ALIGNED || i == 0) && gs != -1 && col % gs == 0) {
           const int n = min(gs, a.d - col);
           // the shared tile is still pristine only at the very first column of the block
           fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, a.mse_steps,
@@ -154,8 +159,8 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
         const float dq = __fmul_rn(scale, __fsub_rn(q, zero));
         const float e = __fdiv_rn(__fsub_rn(x, dq), Us[ci * BLK + ci]);
         er[i] = e;
-        a.codesT[(long long)col * a.out + row] = (unsigned short)q;
-        a.ErrT[(long long)ci * a.lde + row] = e;
+        code_out[(long long)ci * a.out] = (unsigned short)q;
+        err_out[(long long)ci * a.lde] = e;
         const float4* up = reinterpret_cast<const float4*>(Us + ci * BLK + cb);
 #pragma unroll
         for (int j4 = (i + 1) / 4; j4 < SUB / 4; ++j4) {
@@ -367,17 +372,25 @@ __global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ code
   }
 }
 
-template <int WARPS>
-int launch_block(const ColArgs& a, cudaStream_t stream) {
+template <int WARPS, bool ALIGNED>
+int launch_block_t(const ColArgs& a, cudaStream_t stream) {
   static bool attr_set = false;
   const int smem = (BLK * BLK + WARPS * 32 * WS) * (int)sizeof(float);
   if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS, ALIGNED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  gptq_block_kernel<WARPS><<<oc_div_up(a.out, WARPS * 32), LOADERS, smem, stream>>>(a);
+  gptq_block_kernel<WARPS, ALIGNED><<<oc_div_up(a.out, WARPS * 32), LOADERS, smem, stream>>>(a);
   OC_CHECK_LAUNCH();
   return OC_OK;
+}
+
+template <int WARPS>
+int launch_block(const ColArgs& a, cudaStream_t stream) {
+  // group starts fall on window starts when the block starts on a multiple of SUB columns and
+  // the group size is a multiple of SUB
+  const bool aligned = a.gs == -1 || (a.gs % SUB == 0 && a.i1 % SUB == 0);
+  return aligned ? launch_block_t<WARPS, true>(a, stream) : launch_block_t<WARPS, false>(a, stream);
 }
 
 long long round4(long long x) { return (x + 3) / 4 * 4; }
