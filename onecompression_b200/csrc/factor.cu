@@ -106,17 +106,16 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
 // Factorisation: 16 x 16 threads, each holding an 8 x 8 sub-block in registers.  The eight
 // columns of a micro-panel are finished inside the one warp that holds that block column
 // (shuffles only), published to shared memory, and every thread to the right applies them as
-// eight rank-1 updates to its registers: one barrier per eight columns.  Inverse: block forward substitution, 8 rows at a time; each thread owns one column
-// (two threads share a column and split the inner dimension).
+// eight rank-1 updates to its registers: one barrier per eight columns.  Inverse: the 8 x 8
+// diagonal blocks are inverted at once, then neighbouring inverted blocks are joined level by
+// level (four levels, two small products each).
 __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
                                                          float* __restrict__ X, long long ldx,
                                                          int k0, int nb, int* __restrict__ status) {
   extern __shared__ __align__(16) float sm[];
   float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
   float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
-  float* colbuf = sm + 2 * NB * (NB + 1);                                          // [128]
-  float (*P)[8][NB] = reinterpret_cast<float (*)[8][NB]>(colbuf + NB);             // [2][8][128]
-  float (*D)[8] = reinterpret_cast<float (*)[8]>(colbuf + NB + 2 * 8 * NB);        // [8][8]
+  float* T = sm + 2 * NB * (NB + 1);                                               // [64 * 64]
   // block column tx of the 16 x 16 grid of 8 x 8 register blocks lives in one half-warp
   const int tid = threadIdx.x, tx = tid >> 4, ty = tid & 15;
   const int r0 = ty * 8, c0 = tx * 8;
@@ -209,58 +208,57 @@ __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, 
     }
   __syncthreads();
 
-  // ---- inverse: rows 8I .. 8I+7 from the rows above ----
-  const int c = tid & (NB - 1), h = tid >> 7;
-  for (int I = 0; I < NB / 8; ++I) {
-    const int i0 = I * 8;
-    if (tid < 8) {
-      // column tid of the inverse of the 8 x 8 diagonal block
-      float x[8];
+  // ---- inverse of L by doubling: the sixteen 8 x 8 diagonal blocks at once, then four levels
+  // that join neighbouring inverted blocks of size s:  X21 = -X22 (L21 X11) ----
+  for (int e = tid; e < NB * (NB + 1); e += 256) (&Y[0][0])[e] = 0.f;
+  __syncthreads();
+  if (tid < NB) {
+    const int i0 = (tid >> 3) * 8, t = tid & 7;     // column t of the inverse of diagonal block i0
+    float x[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        float acc = (r == tid) ? 1.f : 0.f;
+    for (int r = 0; r < 8; ++r) {
+      float acc = (r == t) ? 1.f : 0.f;
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          if (q < r) acc = fmaf(-S[i0 + r][i0 + q], x[q], acc);
-        x[r] = (r >= tid) ? acc / S[i0 + r][i0 + r] : 0.f;
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) D[r][tid] = x[r];
-    }
-    float t[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) t[r] = 0.f;
-    if (c < i0) {
-      const int half = i0 / 2;
-      int klo = h ? half : 0;
-      const int khi = h ? i0 : half;
-      klo = max(klo, c);      // Y[k][c] = 0 for k < c
-      for (int k = klo; k < khi; ++k) {
-        const float yk = Y[k][c];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) t[r] = fmaf(S[i0 + r][k], yk, t[r]);
-      }
+      for (int q = 0; q < 8; ++q)
+        if (q < r) acc = fmaf(-S[i0 + r][i0 + q], x[q], acc);
+      x[r] = (r >= t) ? acc / S[i0 + r][i0 + r] : 0.f;
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r) P[h][r][c] = t[r];
+    for (int r = 0; r < 8; ++r) Y[i0 + r][i0 + t] = x[r];
+  }
+  __syncthreads();
+  for (int sz = 8; sz < NB; sz *= 2) {
+    // (NB / (2 sz)) problems of sz x sz elements; a thread takes strips of four rows of one column,
+    // i.e. four independent sums per pass over k
+    const int strips = (NB / 8) * sz;
+    const int lg = 31 - __clz(sz);
+    for (int e = tid; e < strips; e += 256) {       // T = L21 * X11 (X11 lower triangular)
+      const int j = e & (sz - 1), i = ((e >> lg) & (sz / 4 - 1)) * 4, m = e >> (2 * lg - 2);
+      const int q0 = 2 * sz * m, mid = q0 + sz;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int k = j; k < sz; ++k) {
+        const float y = Y[q0 + k][q0 + j];
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii) acc[ii] = fmaf(S[mid + i + ii][q0 + k], y, acc[ii]);
+      }
+#pragma unroll
+      for (int ii = 0; ii < 4; ++ii) T[(m << (2 * lg)) + ((i + ii) << lg) + j] = acc[ii];
+    }
     __syncthreads();
-    if (h == 0) {
-      if (c < i0) {
-        float s8[8];
+    for (int e = tid; e < strips; e += 256) {       // X21 = -X22 * T (X22 lower triangular)
+      const int j = e & (sz - 1), i = ((e >> lg) & (sz / 4 - 1)) * 4, m = e >> (2 * lg - 2);
+      const int q0 = 2 * sz * m, mid = q0 + sz;
+      const float* tcol = T + (m << (2 * lg)) + j;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int k = 0; k < i + 4; ++k) {              // X22[i + ii][k] = 0 for k > i + ii
+        const float t = tcol[k << lg];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) s8[r] = P[0][r][c] + P[1][r][c];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          float acc = 0.f;
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            if (q <= r) acc = fmaf(D[r][q], s8[q], acc);
-          Y[i0 + r][c] = -acc;
-        }
-      } else {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) Y[i0 + r][c] = (c < i0 + 8) ? D[r][c - i0] : 0.f;
+        for (int ii = 0; ii < 4; ++ii) acc[ii] = fmaf(Y[mid + i + ii][mid + k], t, acc[ii]);
       }
+#pragma unroll
+      for (int ii = 0; ii < 4; ++ii) Y[mid + i + ii][q0 + j] = -acc[ii];
     }
     __syncthreads();
   }
@@ -317,7 +315,7 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
 
   // ---- blocked right-looking Cholesky --------------------------------------------------
   static bool attr_set = false;
-  const int smem = (2 * NB * (NB + 1) + NB + 2 * 8 * NB + 64) * (int)sizeof(float);
+  const int smem = (2 * NB * (NB + 1) + (NB / 2) * (NB / 2)) * (int)sizeof(float);
   if (!attr_set) {
     OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
