@@ -112,8 +112,9 @@ class ShardedContext:
         first, last = row_slab(out_features, self.rank, self.world)
         slab = weight[first:last]
 
+        default_compute = compute is None
         if compute is None:
-            def compute(w_slab, cross):
+            def compute(w_slab, cross, w_hat_out=None):
                 if w_slab.shape[0] == 0:
                     groups = 1 if gs == -1 else (d + gs - 1) // gs
                     dev = w_slab.device
@@ -126,14 +127,27 @@ class ShardedContext:
                     }
                 if cross is not None:
                     kernels.qep_adjust(w_slab, cross, factor, cfg.perccorr)
+                outputs = {"dequantized": w_hat_out} if w_hat_out is not None else None
                 return kernels.gptq_quantize(w_slab, factor, wbits=bits, groupsize=gs, sym=quantizer.sym,
-                                             blocksize=quantizer.blocksize, pack=True)
+                                             blocksize=quantizer.blocksize, pack=True, outputs=outputs,
+                                             mse=bool(quantizer.mse), q_grid=quantizer.q_grid,
+                                             q_norm=quantizer.q_norm)
 
-        local = compute(slab, c)
+        # Equal slabs on NCCL: the column loop writes this rank's rows of the propagated weight
+        # straight into its place in the all-gather buffer and the gather runs in place.
+        w_full = None
+        if (default_compute and weight.is_cuda and dist.get_backend(self.group) == "nccl"
+                and out_features % (32 * self.world) == 0):
+            w_full = torch.empty((out_features, d), dtype=weight.dtype, device=weight.device)
+            local = compute(slab, c, w_full[first:last])
+            dist.all_gather_into_tensor(w_full, w_full[first:last], group=self.group)
+            w_hat = w_full
+        else:
+            local = compute(slab, c)
+            w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
         qweight = self.gather_rows(local["qweight"], out_features, dim=1)
         qzeros = self.gather_rows(local["qzeros"], out_features, dim=1, per_row=bits / 32.0)
         scales = self.gather_rows(local["scales"], out_features, dim=1)
-        w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
         perm = getattr(factor, "perm", None) if quantizer.actorder else None
         pieces, r0 = [], 0
         for r in rows:
