@@ -124,6 +124,9 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         args.gpus = world
+    # torchrun pins every rank to one host thread; the host side (copies of the results out of the
+    # page-locked staging buffer) wants a fair share of the cores instead
+    torch.set_num_threads(max(1, min(16, (os.cpu_count() or 1) // max(1, world))))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     ctx = None
