@@ -531,36 +531,118 @@ def swiglu_f16(gate: torch.Tensor, up: torch.Tensor, inplace: bool = False) -> t
     return y
 
 
-_staging = {"buf": None}
+class _HostCopier:
+    """Device -> host copies of result tensors through two reusable page-locked staging buffers.
+
+    A layer's results are a handful of small tensors: copied one by one into pageable memory each
+    costs a device synchronisation and runs at a fraction of the link speed, and page-locking fresh
+    memory for every result is slower still.  So the tensors are packed into a staging buffer with
+    asynchronous copies, and a worker thread moves them on into ordinary host tensors once the
+    copies have landed.  In deferred mode the caller does not wait for that: it gets the
+    destination tensors at once and calls ``finish`` before anyone reads them."""
+
+    def __init__(self):
+        import queue
+        import threading
+
+        self._bufs = [None, None]
+        self._busy = [None, None]        # threading.Event of the job that last used each buffer
+        self._next = 0
+        self._jobs = queue.Queue()
+        self._pending = []
+        self._error = None
+        self._thread = None
+        self._threading = threading
+        self.deferred = False
+
+    def _worker(self):
+        while True:
+            job = self._jobs.get()
+            if job is None:
+                return
+            event, pairs, done = job
+            try:
+                event.synchronize()
+                for dst, src in pairs:
+                    dst.copy_(src)
+            except Exception as exc:  # noqa: BLE001 - handed to the caller in finish()
+                self._error = exc
+            finally:
+                done.set()
+
+    def submit(self, tensors):
+        todo = [(i, t) for i, t in enumerate(tensors) if t is not None and t.is_cuda]
+        outs = list(tensors)
+        if not todo:
+            return outs
+        if self._thread is None or not self._thread.is_alive():
+            self._thread = self._threading.Thread(target=self._worker, daemon=True)
+            self._thread.start()
+        sizes = [(t.numel() * t.element_size() + 255) // 256 * 256 for _, t in todo]
+        total = sum(sizes)
+        slot = self._next
+        self._next ^= 1
+        if self._busy[slot] is not None:
+            self._busy[slot].wait()      # the job that used this staging buffer before has drained it
+        buf = self._bufs[slot]
+        if buf is None or buf.numel() < total:
+            buf = torch.empty(max(total, 64 << 20), dtype=torch.uint8, pin_memory=True)
+            self._bufs[slot] = buf
+        pairs, off = [], 0
+        for (i, t), sz in zip(todo, sizes):
+            nbytes = t.numel() * t.element_size()
+            view = buf[off : off + nbytes].view(t.dtype).view(t.shape)
+            view.copy_(t.contiguous(), non_blocking=True)
+            dst = torch.empty(t.shape, dtype=t.dtype)
+            pairs.append((dst, view))
+            outs[i] = dst
+            off += sz
+        event = torch.cuda.Event()
+        event.record()
+        done = self._threading.Event()
+        self._busy[slot] = done
+        self._pending.append(done)
+        self._jobs.put((event, pairs, done))
+        if not self.deferred:
+            self.finish()
+        return outs
+
+    def finish(self):
+        for done in self._pending:
+            done.wait()
+        self._pending = []
+        if self._error is not None:
+            exc, self._error = self._error, None
+            raise exc
+
+
+_copier = _HostCopier()
 
 
 def to_host(tensors):
-    """Copy device tensors to ordinary host tensors through one reusable page-locked staging
-    buffer and a single synchronisation (None entries pass through).  A layer's results are a
-    handful of small tensors: copied one by one into pageable memory each costs a device
-    synchronisation and runs at a fraction of the link speed, and page-locking fresh memory for
-    every result is slower still."""
-    todo = [(i, t) for i, t in enumerate(tensors) if t is not None and t.is_cuda]
-    outs = list(tensors)
-    if not todo:
-        return outs
-    sizes = [(t.numel() * t.element_size() + 255) // 256 * 256 for _, t in todo]
-    total = sum(sizes)
-    buf = _staging["buf"]
-    if buf is None or buf.numel() < total:
-        buf = torch.empty(max(total, 64 << 20), dtype=torch.uint8, pin_memory=True)
-        _staging["buf"] = buf
-    views, off = [], 0
-    for (i, t), sz in zip(todo, sizes):
-        nbytes = t.numel() * t.element_size()
-        v = buf[off : off + nbytes].view(t.dtype).view(t.shape)
-        v.copy_(t.contiguous(), non_blocking=True)
-        views.append(v)
-        off += sz
-    torch.cuda.current_stream().synchronize()
-    for (i, _), v in zip(todo, views):
-        outs[i] = v.clone()
-    return outs
+    """Copy device tensors to ordinary host tensors (None entries pass through).  Outside a
+    ``deferred_host_copies`` block the returned tensors are complete; inside, they are filled in the
+    background and complete when the block ends (or after ``finish_host_copies``)."""
+    return _copier.submit(tensors)
+
+
+def finish_host_copies():
+    _copier.finish()
+
+
+class deferred_host_copies:
+    """Context manager: ``to_host`` calls inside return at once; everything is complete on exit."""
+
+    def __enter__(self):
+        self._previous = _copier.deferred
+        _copier.deferred = True
+        return self
+
+    def __exit__(self, *exc):
+        _copier.deferred = self._previous
+        if not _copier.deferred:
+            _copier.finish()
+        return False
 
 
 def set_gemm_engine(mode: int) -> int:

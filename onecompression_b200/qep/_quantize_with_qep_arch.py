@@ -583,7 +583,12 @@ class BlockQuantizer:
         """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
         target layers end up holding their dequantized weights.  With ``next_block`` (the block
         the following call will process, already on the device and unmodified) its
-        full-precision pass is started on a side stream as soon as its inputs exist."""
+        full-precision pass is started on a side stream as soon as its inputs exist.
+        The layers' results travel to the host in the background and are complete on return."""
+        with kernels.deferred_host_copies():
+            return self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+
+    def _run_block(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None, next_block=None):
         qz, dev, bs = self.quantizer, self.device, self.batch_size
         t0 = self._tick(None, 0.0)
         fp = self._take_prefetched(block_q)

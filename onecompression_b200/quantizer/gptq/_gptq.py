@@ -357,8 +357,8 @@ class GPTQ(Quantizer):
                 pieces += [out["codes"][r0:r0 + r], out["zeros"][:, r0:r0 + r]]
             pieces.append(out["scales"][:, r0:r0 + r])
             r0 += r
-        host = kernels.to_host(pieces + [perm])
-        perm_host = host[-1]
+        host = kernels.to_host(pieces + [perm] * len(rows))     # may still be in flight: do not read here
+        torch.cuda.synchronize(stacked.device)
         elapsed = time.time() - t0
         results, r0 = {}, 0
         for i, (m, r) in enumerate(zip(modules, rows)):
@@ -369,7 +369,7 @@ class GPTQ(Quantizer):
                     qzeros = qzeros.reshape(r, 1)
             res = GPTQResult(
                 wbits=bits, groupsize=gs, actorder=self.actorder, sym=self.sym, qweight=qweight, scales=scales,
-                qzeros=qzeros, perm=perm_host.clone() if perm_host is not None else None,
+                qzeros=qzeros, perm=host[3 * len(rows) + i],
                 qweight_is_packed=packed, qzeros_is_packed=packed, qweight_original_shape=(r, d),
             )
             res.__dict__["_device_dequantized"] = out["dequantized"][r0:r0 + r]

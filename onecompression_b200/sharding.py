@@ -155,9 +155,10 @@ class ShardedContext:
             r0 += r
         perm64 = perm.to(torch.int64) if perm is not None else None
         if qweight.is_cuda:
-            host = kernels.to_host(pieces + [perm64])
+            host = kernels.to_host(pieces + [perm64] * len(rows))   # may still be in flight: not read here
         else:
-            host = [p.contiguous() for p in pieces] + [perm64]
+            host = [p.contiguous() for p in pieces] + [perm64.clone() if perm64 is not None else None
+                                                       for _ in rows]
         if weight.is_cuda:
             torch.cuda.synchronize(weight.device)
         elapsed = time.time() - t0
@@ -167,7 +168,7 @@ class ShardedContext:
             result = GPTQResult(
                 wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
                 qweight=qw, scales=(sc if gs != -1 else sc.reshape(r, 1)), qzeros=qz,
-                perm=host[-1].clone() if host[-1] is not None else None,
+                perm=host[3 * len(rows) + i],
                 qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(r, d),
             )
             result.__dict__["_device_dequantized"] = w_hat[r0:r0 + r]
