@@ -1,1 +1,2 @@
-from ._autobit import AutoBitQuantizer, effective_bits_per_param, solve_assignment  # noqa: F401
+from ._autobit import (AutoBitQuantizer, collect_activation_stats, effective_bits_per_param,  # noqa: F401
+                       solve_assignment)

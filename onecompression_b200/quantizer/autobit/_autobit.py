@@ -9,8 +9,8 @@ reference hands this multiple-choice knapsack to OR-Tools' SCIP; this module sol
 with a Pareto dynamic programme (the candidate costs are integers once multiplied by the group
 sizes), so it needs no solver package.  The RTN errors are computed on the GPU.
 
-Not covered here: the curvature statistics of the reference's activation-aware strategy (they
-need backward passes through the model) and the DBF fallback for budgets below 2 bits.
+``collect_activation_stats`` gathers the two diagonals of the activation-aware cost with forward
+and backward hooks.  Not covered here: the DBF fallback for budgets below 2 bits.
 """
 
 from __future__ import annotations
@@ -38,6 +38,65 @@ def effective_bits_per_param(wbits, group_size=128, scale_bits=16, zero_bits=Non
     if in_features is not None and in_features > 0:
         return wbits + meta / in_features
     return float(wbits)
+
+
+def collect_activation_stats(model, input_ids, candidates, batch_size=4, use_curvature_b=True):
+    """Diagonal statistics of the activation-aware cost (reference
+    onecomp/quantizer/autobit/activation_stats.py:75-282): for every candidate layer
+    a[name] = E_tokens[x_p²] over its input channels and, with ``use_curvature_b``,
+    b[name] = E_tokens[(∂L/∂y_q)²] over its output channels, L being the mean next-token
+    cross-entropy of each calibration sequence taken on its own.
+
+    ``candidates`` is a list of (name, module); ``input_ids`` [n_seq, seq] lives on the model's
+    device.  The whole model is differentiated at once (the reference walks block by block to fit
+    large models in memory; the statistics are the same).  Returns (a, b) dicts of fp32 tensors on
+    the CPU; b[name] is None without curvature."""
+    import torch.nn.functional as F
+
+    a_acc = {n: torch.zeros(m.weight.shape[1], dtype=torch.float64) for n, m in candidates}
+    b_acc = {n: torch.zeros(m.weight.shape[0], dtype=torch.float64) for n, m in candidates}
+    counts = {n: 0 for n, _ in candidates}
+    hooks = []
+
+    def fwd(name):
+        def hook(_m, inp, _out):
+            x = inp[0].detach().float().reshape(-1, inp[0].shape[-1])
+            a_acc[name] += x.pow(2).sum(0).double().cpu()
+            counts[name] += x.shape[0]
+        return hook
+
+    def bwd(name):
+        def hook(_m, _gin, gout):
+            if gout[0] is not None:
+                g = gout[0].detach().float().reshape(-1, gout[0].shape[-1])
+                b_acc[name] += g.pow(2).sum(0).double().cpu()
+        return hook
+
+    for name, module in candidates:
+        hooks.append(module.register_forward_hook(fwd(name)))
+        if use_curvature_b:
+            hooks.append(module.register_full_backward_hook(bwd(name)))
+    flags = {p: p.requires_grad for p in model.parameters()}
+    try:
+        for p in flags:
+            p.requires_grad_(use_curvature_b)
+        for first in range(0, input_ids.shape[0], batch_size):
+            ids = input_ids[first:first + batch_size]
+            with torch.set_grad_enabled(use_curvature_b):
+                logits = model(input_ids=ids).logits
+                if use_curvature_b:
+                    per_tok = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(),
+                                              ids[:, 1:].reshape(-1), reduction="none")
+                    per_tok.view(ids.shape[0], -1).mean(1).sum().backward()
+            model.zero_grad(set_to_none=True)
+    finally:
+        for h in hooks:
+            h.remove()
+        for p, f in flags.items():
+            p.requires_grad_(f)
+    a = {n: (a_acc[n] / max(counts[n], 1)).float() for n in a_acc}
+    b = {n: ((b_acc[n] / max(counts[n], 1)).float() if use_curvature_b else None) for n in b_acc}
+    return a, b
 
 
 def solve_assignment(errors, params, eff_bits, target_bit, fused_groups=None, max_states=400000):
@@ -121,6 +180,9 @@ class AutoBitQuantizer(Quantizer):
     target_bit_is_effective: bool = False
     input_moments: dict = None
     output_curvature: dict = None
+    calibration_input_ids: torch.Tensor = None     # used to collect the two statistics when absent
+    use_curvature_b: bool = True
+    stats_batch_size: int = 4
     bitpack_on_quantize: bool = True
     fused_groups: list = field(default_factory=lambda: [
         ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"],
@@ -241,6 +303,12 @@ class AutoBitQuantizer(Quantizer):
                         break
         else:
             cands = self._candidates(model)
+            if (self.assignment_strategy == "activation_aware" and self.input_moments is None
+                    and self.calibration_input_ids is not None):
+                self.input_moments, self.output_curvature = collect_activation_stats(
+                    model, self.calibration_input_ids, cands, self.stats_batch_size, self.use_curvature_b)
+                if not self.use_curvature_b:
+                    self.output_curvature = None
             target = self.target_bit if self.target_bit_is_effective else self._effective_target(cands)
             self.effective_target_bit = target
             errors = [self._rtn_errors(n, m) for n, m in cands]

@@ -69,3 +69,37 @@ def test_model_scale_instance_solves_fast():
     used = sum(eff[m][chosen[m]] * params[m] for m in range(len(params))) / sum(params)
     assert used <= 3.5 + 19.5 / 128 + 1e-9 and used > 3.3
     assert len(set(chosen)) > 1
+
+
+def test_activation_stats_on_cpu_model():
+    """a = E[x²] per input channel and b = E[(dL/dy)²] per output channel, against a direct
+    computation on a tiny fp32 Llama (no GPU involved: hooks and autograd only)."""
+    import torch
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200.quantizer.autobit import collect_activation_stats
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=32, intermediate_size=64, num_attention_heads=2, num_key_value_heads=2,
+                      num_hidden_layers=1, vocab_size=64, max_position_embeddings=32)
+    model = LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, 64, (5, 12))
+    cands = [(n, m) for n, m in model.named_modules() if isinstance(m, torch.nn.Linear) and "lm_head" not in n]
+    a, b = collect_activation_stats(model, ids, cands, batch_size=2)
+    assert len(a) == 7 and all(not p.requires_grad or True for p in model.parameters())
+    name, mod = cands[3]        # o_proj
+    xs, gs = [], []
+    h1 = mod.register_forward_hook(lambda m, i, o: xs.append(i[0].detach()))
+    h2 = mod.register_full_backward_hook(lambda m, gi, go: gs.append(go[0].detach()))
+    for p in model.parameters():
+        p.requires_grad_(True)
+    for i in range(5):          # one sequence at a time, each with its own mean loss
+        out = model(input_ids=ids[i:i + 1], labels=ids[i:i + 1])
+        out.loss.backward()
+        model.zero_grad()
+    h1.remove(); h2.remove()
+    x = torch.cat([t.reshape(-1, t.shape[-1]) for t in xs]); g = torch.cat([t.reshape(-1, t.shape[-1]) for t in gs])
+    assert torch.allclose(a[name], x.pow(2).mean(0), rtol=1e-4, atol=1e-8)
+    assert torch.allclose(b[name], g.pow(2).mean(0), rtol=1e-3, atol=1e-12)
+    a2, b2 = collect_activation_stats(model, ids, cands, batch_size=5, use_curvature_b=False)
+    assert all(v is None for v in b2.values()) and torch.allclose(a2[name], a[name], rtol=1e-5)

