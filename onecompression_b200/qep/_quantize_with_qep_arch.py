@@ -714,6 +714,7 @@ class BlockQuantizer:
 
         if experts:
             per_module = _compute_per_module_hessians(block_q, experts, inps_q, kwargs, bs, dev, self.dist)
+            shared = []
             for module in experts:
                 name = qz.module_to_name[module]
                 entry = per_module[module]
@@ -732,9 +733,27 @@ class BlockQuantizer:
                         if on_layer_done is not None:
                             on_layer_done(f"{name}, skipped: no tokens")
                     continue
+                child = _gptq_of(qz, module)
+                if self.dist is not None and child is not None and child.bitpack_on_quantize:
+                    shared.append((module, child, entry[0]))     # dealt to the ranks below
+                    continue
                 self._quantize_one(module, name, entry[0], None, entry[1], None)
                 if on_layer_done is not None:
                     on_layer_done(name)
+            # experts are independent problems: whole layers per rank instead of row slabs
+            by_child = {}
+            for module, child, h_e in shared:
+                by_child.setdefault(id(child), (child, []))[1].append((module, h_e))
+            for child, items in by_child.values():
+                done = self.dist.quantize_independent(child, items)
+                for module, _h in items:
+                    name = qz.module_to_name[module]
+                    if child is not qz:
+                        child.results.pop(name, None)
+                    qz.results[name] = done[module]
+                    self._install_dequantized(module, name)
+                    if on_layer_done is not None:
+                        on_layer_done(name)
 
         next_q = torch.empty_like(inps_q)
         if memo is not None and not experts:

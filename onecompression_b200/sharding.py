@@ -177,3 +177,85 @@ class ShardedContext:
             results[m] = result
             r0 += r
         return results
+
+    # ---- independent layers (MoE experts) ---------------------------------------------
+    def quantize_independent(self, quantizer, items, compute: Optional[Callable] = None):
+        """Layers with a Hessian of their own (experts of a mixture, each calibrated on the tokens
+        routed to it) are independent problems: they are dealt round-robin to the ranks, each rank
+        factors and quantizes its layers whole, and the results are broadcast from their owners so
+        that every rank holds every GPTQResult and every propagated weight.
+
+        ``items``: list of (module, hessian) with the Hessian already reduced over the ranks, in the
+        same order on every rank.  ``compute(weight, hessian) -> dict`` (qweight, qzeros, scales,
+        dequantized, optionally perm) replaces the CUDA kernels in CPU tests.
+        Returns {module: GPTQResult}; ``quantizer.results`` is filled as well."""
+        import time
+
+        from . import kernels
+        from .quantizer.gptq._gptq import GPTQ, GPTQResult
+
+        if compute is None:
+            def compute(weight, hessian):
+                factor = kernels.factor_hessian(hessian, quantizer.percdamp, quantizer.actorder)
+                out = kernels.gptq_quantize(weight, factor, wbits=bits, groupsize=gs, sym=quantizer.sym,
+                                            blocksize=quantizer.blocksize, pack=True, mse=bool(quantizer.mse),
+                                            q_grid=quantizer.q_grid, q_norm=quantizer.q_norm)
+                if quantizer.actorder:
+                    out["perm"] = factor.perm.to(torch.int64)
+                return out
+
+        results = {}
+        local = {}
+        t_local = {}
+        for i, (module, hessian) in enumerate(items):
+            if i % self.world != self.rank:
+                continue
+            name = quantizer.module_to_name[module]
+            bits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
+            gs = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
+            t0 = time.time()
+            local[i] = compute(module.weight.data, hessian)
+            if module.weight.is_cuda:
+                torch.cuda.synchronize(module.weight.device)
+            t_local[i] = time.time() - t0
+        for i, (module, _h) in enumerate(items):
+            owner = i % self.world
+            name = quantizer.module_to_name[module]
+            bits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
+            gs = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
+            out_features, d = module.weight.shape
+            groups = 1 if gs == -1 else (d + gs - 1) // gs
+            dev = module.weight.device
+            shapes = {
+                "qweight": ((d * bits // 32, out_features), torch.int32),
+                "qzeros": ((groups, out_features * bits // 32), torch.int32),
+                "scales": ((groups, out_features), torch.float16),
+                "dequantized": ((out_features, d), module.weight.dtype),
+            }
+            if quantizer.actorder:
+                shapes["perm"] = ((d,), torch.int64)
+            got = {}
+            for key, (shape, dtype) in shapes.items():
+                if owner == self.rank:
+                    buf = local[i][key].to(device=dev, dtype=dtype).contiguous()
+                else:
+                    buf = torch.empty(shape, dtype=dtype, device=dev)
+                dist.broadcast(buf, src=dist.get_global_rank(self.group, owner) if self.group is not None else owner,
+                               group=self.group)
+                got[key] = buf
+            elapsed = torch.tensor([t_local.get(i, 0.0)], dtype=torch.float64, device=dev)
+            dist.broadcast(elapsed, src=dist.get_global_rank(self.group, owner) if self.group is not None else owner,
+                           group=self.group)
+            pieces = [got["qweight"], got["scales"], got["qzeros"], got.get("perm")]
+            host = kernels.to_host(pieces) if dev.type == "cuda" else pieces
+            result = GPTQResult(
+                wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym, qweight=host[0],
+                scales=(host[1] if gs != -1 else host[1].reshape(out_features, 1)), qzeros=host[2], perm=host[3],
+                qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(out_features, d),
+            )
+            result.__dict__["_device_dequantized"] = got["dequantized"]
+            result.quantization_time = float(elapsed.item())
+            quantizer.results[name] = result
+            results[module] = result
+            local.pop(i, None)
+        return results

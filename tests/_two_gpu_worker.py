@@ -92,6 +92,37 @@ def main(out_dir):
     a, b = seq_shard(48, rank, world)
     rel = ((nq_s.float() - nq_1[a:b].float()).norm() / nq_1[a:b].float().norm()).item()
     assert rel < 0.05, rel
+
+    # 4. a mixture-of-experts block: experts are dealt whole to the ranks and broadcast from their
+    # owners.  Both ranks feed the same tokens, so the reduced Hessians equal the single-GPU ones
+    # exactly and every result must be bit-identical to the single-GPU run.
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_gpu_driver import _TinyMoEBlock
+
+    def run_moe(ctx):
+        torch.manual_seed(0)
+        blk = _TinyMoEBlock(64, 128, 4).half().to(dev)
+        for p in blk.parameters():
+            p.data.normal_(0, 0.05)
+        gen = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(32, 64, 64, device=dev, generator=gen).half()
+        q = GPTQ(wbits=4, groupsize=32, sym=False, exclude_layer_keywords=["router"])
+        for n, m in blk.named_modules():
+            if isinstance(m, torch.nn.Linear) and "router" not in n:
+                q.module_to_name[m] = f"model.layers.0.{n}"
+        runner = BlockQuantizer(q, QEPConfig(device=str(dev)), batch_size=16, device=dev, dist=ctx)
+        nq, _ = runner.run(blk, x.clone(), x.clone(), {})
+        return q.results, nq
+
+    moe_s, nq_ms = run_moe(ctx)
+    moe_1, nq_m1 = run_moe(None)
+    assert set(moe_s) == set(moe_1) and len(moe_1) == 9
+    for name, r in moe_1.items():
+        s = moe_s[name]
+        assert s.qweight_is_packed == r.qweight_is_packed, name
+        for f in ("qweight", "qzeros", "scales"):
+            assert torch.equal(getattr(s, f), getattr(r, f)), (name, f)
+    assert torch.equal(nq_ms, nq_m1)
     dist.barrier()
     if rank == 0:
         open(os.path.join(out_dir, "ok"), "w").write(f"{frac} {rel}")

@@ -104,6 +104,37 @@ def _worker(rank, world, port, out_dir):
         assert np.array_equal(r.qzeros.numpy(), alone["qzeros"].numpy())
         assert torch.equal(r.scales, alone["scales"])
         assert torch.equal(r.__dict__["_device_dequantized"], alone["dequantized"])
+
+    # independent layers (experts): dealt round-robin, results broadcast from their owners
+    experts, items = [], []
+    q3 = GPTQ(wbits=4, groupsize=32, sym=False)
+    for e in range(5):
+        lin_e = torch.nn.Linear(d, 64, bias=False).half()
+        lin_e.weight.data = (torch.randn(64, d, generator=g) * 0.02).half()
+        h_e = h_all * (1.0 + 0.1 * e)
+        q3.module_to_name[lin_e] = f"expert{e}"
+        experts.append(lin_e)
+        items.append((lin_e, h_e))
+    calls = []
+
+    def compute_whole(weight, hessian):
+        calls.append(1)
+        r = orc.gptq_quantize(weight, hessian.clone(), wbits=4, groupsize=32, sym=False)
+        qw, qz = orc.pack_result(r["qweight"].numpy(), r["qzeros"].numpy(), 4)
+        deq = orc.dequantize_result(qw, r["scales"], qz, None, 4, 32, weight.shape)
+        return {"qweight": torch.from_numpy(qw), "qzeros": torch.from_numpy(qz), "scales": r["scales"],
+                "dequantized": deq}
+
+    done = ctx.quantize_independent(q3, items, compute=compute_whole)
+    assert len(calls) == len([i for i in range(5) if i % world == rank])      # only the owned layers
+    for lin_e, h_e in items:
+        alone = compute_whole(lin_e.weight.data, h_e)
+        r = done[lin_e]
+        assert np.array_equal(r.qweight.numpy(), alone["qweight"].numpy())
+        assert np.array_equal(r.qzeros.numpy(), alone["qzeros"].numpy())
+        assert torch.equal(r.scales, alone["scales"])
+        assert torch.equal(r.__dict__["_device_dequantized"], alone["dequantized"])
+        assert q3.results[q3.module_to_name[lin_e]] is r
     open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     dist.destroy_process_group()
 
