@@ -445,6 +445,7 @@ class BlockQuantizer:
         self.fuse_rmsnorm = fuse_rmsnorm
         self.fuse_elementwise = fuse_elementwise
         self.stack_layers = stack_layers
+        self._stream_io = None
         # with profile=True every phase is bracketed by device synchronisation and its wall
         # time is added to self.timings (seconds per phase name); off by default
         self.profile = profile
@@ -509,6 +510,7 @@ class BlockQuantizer:
         block_f = copy.deepcopy(block)
         names = {m: n for n, m in block.named_modules() if isinstance(m, nn.Linear)}
         mods_f = {n: m for n, m in block_f.named_modules() if isinstance(m, nn.Linear)}
+        self._io("before_read_f", 0, 1)
         regular, _experts = self._classify(block, make_grouped_module(block, inps_f, kwargs, dev))
         heads, need_c = [], {}
         for group in regular:
@@ -538,8 +540,10 @@ class BlockQuantizer:
             with _FusedOps([block_f], self.fuse_rmsnorm, self.fuse_elementwise):
                 for first in range(0, n_seq, bs):
                     cursor["first"] = first
+                    self._io("before_read_f", first, min(bs, n_seq - first))
                     y = call_block(block_f, inps_f[first : first + bs].to(dev), kwargs)
                     next_f[first : first + bs].copy_(y)
+                    self._io("after_write_f", first, min(bs, n_seq - first), next_f)
         finally:
             for h in handles:
                 h.remove()
@@ -578,15 +582,31 @@ class BlockQuantizer:
             p_.data.record_stream(main)
         return res
 
+    def _io(self, what, *args):
+        """Chunk-level notifications for a caller that streams activations from / to the host."""
+        fn = getattr(self._stream_io, what, None) if self._stream_io is not None else None
+        if fn is not None:
+            fn(*args)
+
     @torch.no_grad()
-    def run(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None, next_block=None):
+    def run(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None, next_block=None, stream_io=None):
         """Returns (next inps_q, next inps_f).  ``block_q`` must be on the device; its
         target layers end up holding their dequantized weights.  With ``next_block`` (the block
         the following call will process, already on the device and unmodified) its
         full-precision pass is started on a side stream as soon as its inputs exist.
-        The layers' results travel to the host in the background and are complete on return."""
-        with kernels.deferred_host_copies():
-            return self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+        The layers' results travel to the host in the background and are complete on return.
+        ``stream_io`` lets a caller move the activations in and out while the block is processed:
+        any of ``before_read_f(first, size)``, ``before_read_q(first, size)`` (called before sequences
+        first..first+size of ``inps_f`` / ``inps_q`` are read for the first time: make the current
+        stream wait for them there), ``after_write_f(first, size, next_f)`` and
+        ``after_write_q(first, size, next_q)`` (called when those sequences of the outputs have been
+        enqueued: start copying them out on another stream)."""
+        self._stream_io = stream_io
+        try:
+            with kernels.deferred_host_copies():
+                return self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+        finally:
+            self._stream_io = None
 
     def _run_block(self, block_q, inps_q, inps_f, kwargs, on_layer_done=None, next_block=None):
         qz, dev, bs = self.quantizer, self.device, self.batch_size
@@ -604,6 +624,7 @@ class BlockQuantizer:
     def _run_quantized(self, block_q, inps_q, inps_f, kwargs, on_layer_done, fp, t0):
         qz, dev, bs = self.quantizer, self.device, self.batch_size
         block_f, mods_f, next_f, use_cache = fp["block_f"], fp["mods_f"], fp["next_f"], fp["use_cache"]
+        self._io("before_read_q", 0, 1)
         groups_q = make_grouped_module(block_q, inps_q, kwargs, dev)
         names_q = {m: n for n, m in block_q.named_modules() if isinstance(m, nn.Linear)}
         regular, experts = self._classify(block_q, groups_q)
@@ -631,6 +652,8 @@ class BlockQuantizer:
                 for first in range(0, n_seq, bs):
                     if memo is not None:
                         memo.set_chunk(first, min(bs, n_seq - first))
+                    if gi == 0:
+                        self._io("before_read_q", first, min(bs, n_seq - first))
                     try:
                         call_block(block_q, inps_q[first : first + bs].to(dev), kwargs)
                     except StopForward:
@@ -763,13 +786,16 @@ class BlockQuantizer:
                     memo.set_chunk(first, min(bs, n_seq - first))
                     y = call_block(block_q, inps_q[first : first + bs].to(dev), kwargs)
                     next_q[first : first + bs].copy_(y)
+                    self._io("after_write_q", first, min(bs, n_seq - first), next_q)
             finally:
                 memo.end_pass(complete=False)
                 memo.release()
         else:
             if memo is not None:
                 memo.release()
+            self._io("before_read_q", 0, n_seq)
             forward_input(inps_q, block_q, kwargs, bs, dev, out=next_q)
+            self._io("after_write_q", 0, n_seq, next_q)
         del block_f
         self._tick("pass_propagate", t0)
         return next_q, next_f

@@ -224,6 +224,8 @@ def test_forward_memo_changes_nothing():
                 q.module_to_name[m] = f"model.layers.0.{n}"
         runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV, memoize=memo)
         nq, nf = runner.run(stack.blocks[0], x0.clone(), x0.clone(), stack.kwargs)
+        # the driver runs without autograd: nothing of the passes may be kept alive for a backward
+        assert nq.grad_fn is None and nf.grad_fn is None and not nq.requires_grad
         outs.append((nq.cpu(), nf.cpu(), {k: (r.qweight, r.scales, r.qzeros) for k, r in q.results.items()}))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     for k in outs[0][2]:
