@@ -654,3 +654,57 @@ def test_autobit_activation_aware_assignment():
         p = f"model.layers.{layer}."
         assert bits_of[p + "self_attn.q_proj"] == bits_of[p + "self_attn.k_proj"] == bits_of[p + "self_attn.v_proj"]
         assert bits_of[p + "mlp.gate_proj"] == bits_of[p + "mlp.up_proj"]
+
+
+def test_gpt_oss_layer_unfused_bf16_through_the_driver():
+    """A (tiny) GPT-OSS decoder layer as transformers builds it: bf16, fused experts un-fused into
+    per-expert linears with bias, attention with sinks.  Regular layers go through QEP, every expert
+    linear gets the Hessian of its own routed tokens and no correction; results agree with the oracle."""
+    from transformers import GptOssConfig
+    from transformers.models.gpt_oss.modeling_gpt_oss import GptOssDecoderLayer, GptOssRotaryEmbedding
+
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+    from onecompression_b200.utils import unfuse_moe_experts
+
+    class Rec(_Recorder, GPTQ):
+        pass
+
+    torch.manual_seed(0)
+    cfg = GptOssConfig(hidden_size=128, intermediate_size=128, num_local_experts=4, num_experts_per_tok=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=32, num_hidden_layers=1,
+                       vocab_size=128, max_position_embeddings=64, layer_types=["full_attention"])
+    layer = GptOssDecoderLayer(cfg, 0)
+    for p in layer.parameters():
+        p.data.normal_(0, 0.05)
+    layer.input_layernorm.weight.data.fill_(1.0)
+    layer.post_attention_layernorm.weight.data.fill_(1.0)
+    assert unfuse_moe_experts(layer) == 1
+    layer = layer.to(torch.bfloat16).to(DEV).eval()
+    seq = 32
+    x0 = torch.randn(48, seq, 128, device=DEV).to(torch.bfloat16)
+    rot = GptOssRotaryEmbedding(cfg).to(DEV)
+    pos = torch.arange(seq, device=DEV).unsqueeze(0)
+    kwargs = {"position_embeddings": rot(x0[:1], pos), "attention_mask": None, "position_ids": pos}
+    q = Rec(wbits=4, groupsize=32, sym=False, exclude_layer_keywords=["router"])
+    q.seen, q.inputs = [], {}
+    for n, m in layer.named_modules():
+        if isinstance(m, torch.nn.Linear) and "router" not in n:
+            q.module_to_name[m] = f"model.layers.0.{n}"
+    assert len(q.module_to_name) == 4 + 12
+    runner = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV)
+    nq, nf = runner.run(layer, x0.clone(), x0.clone(), kwargs)
+    assert nq.dtype == torch.bfloat16 and torch.isfinite(nq.float()).all()
+    assert set(q.results) == set(q.module_to_name.values())
+    matched = total = 0
+    for name, (h, c, w_before) in q.inputs.items():
+        expert = ".experts." in name
+        assert (c is None) == expert, name                       # no weight correction for experts
+        w_adj = w_before if c is None else orc.qep_adjust_weight(w_before, h, c, 0.01, 0.5)
+        ref = orc.gptq_quantize(w_adj, h.clone(), wbits=4, groupsize=32, sym=False)
+        eq = _codes(q.results[name]) == ref["qweight"].numpy()
+        matched += int(eq.sum())
+        total += eq.size
+    assert total > 0 and matched / total >= 0.99, matched / total
+    for m, name in q.module_to_name.items():
+        assert m.weight.dtype == torch.bfloat16
