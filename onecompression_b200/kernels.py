@@ -237,6 +237,43 @@ def factor_hessian(h: torch.Tensor, percdamp: float, actorder: bool, max_retries
     )
 
 
+def factor_hessian_launch(h: torch.Tensor, percdamp: float, actorder: bool) -> dict:
+    """First attempt of ``factor_hessian`` enqueued on the current stream without waiting for its
+    status: lets several small factorisations run side by side on different streams.  Finish
+    with ``factor_hessian_resolve``."""
+    _require_cuda(h, "hessian")
+    if h.dtype != torch.float32:
+        h = h.float()
+    if h.stride(1) != 1:
+        h = h.contiguous()
+    d = h.shape[0]
+    dev = h.device
+    out = {
+        "h": h, "u": torch.empty((d, d), dtype=torch.float32, device=dev),
+        "perm": torch.empty(d, dtype=torch.int32, device=dev),
+        "invperm": torch.empty(d, dtype=torch.int32, device=dev),
+        "dead": torch.empty(d, dtype=torch.uint8, device=dev),
+        "damp": torch.empty(2, dtype=torch.float32, device=dev),
+        "status": torch.empty(1, dtype=torch.int32, device=dev),
+        "percdamp": float(percdamp), "actorder": bool(actorder),
+    }
+    with torch.cuda.device(dev):
+        ws = _workspace(_lib.load().oc_hinv_workspace_bytes(d), dev)
+        call("oc_hinv_factor", ptr(h), h.stride(0), d, float(percdamp), 1.0, 1 if actorder else 0, 0,
+             ptr(out["u"]), d, ptr(out["perm"]), ptr(out["invperm"]), ptr(out["dead"]), ptr(out["damp"]),
+             ptr(out["status"]), ptr(ws), ws.numel(), stream_handle())
+    return out
+
+
+def factor_hessian_resolve(pending: dict, max_retries: int = 5) -> HessianFactor:
+    """Waits for a launched factorisation; a failed first attempt goes through the retry rule of
+    ``factor_hessian`` on the current stream."""
+    if int(pending["status"].item()) == 0:
+        return HessianFactor(pending["u"], pending["perm"], pending["invperm"], pending["dead"], pending["damp"],
+                             pending["actorder"], pending["percdamp"], 1.0, 1)
+    return factor_hessian(pending["h"], pending["percdamp"], pending["actorder"], max_retries)
+
+
 # ---------------------------------------------------------------------------
 # GPTQ column loop
 # ---------------------------------------------------------------------------

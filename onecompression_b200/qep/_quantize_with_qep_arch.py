@@ -757,18 +757,23 @@ class BlockQuantizer:
                             on_layer_done(f"{name}, skipped: no tokens")
                     continue
                 child = _gptq_of(qz, module)
-                if self.dist is not None and child is not None and child.bitpack_on_quantize:
-                    shared.append((module, child, entry[0]))     # dealt to the ranks below
+                if (child is not None and child.stack_key(module) is not None
+                        and (self.dist is None or child.bitpack_on_quantize)):
+                    shared.append((module, child, entry[0]))     # quantized together below
                     continue
                 self._quantize_one(module, name, entry[0], None, entry[1], None)
                 if on_layer_done is not None:
                     on_layer_done(name)
-            # experts are independent problems: whole layers per rank instead of row slabs
+            # experts are independent small problems: several at a time on separate streams, and
+            # whole layers per rank instead of row slabs when there are ranks
             by_child = {}
             for module, child, h_e in shared:
                 by_child.setdefault(id(child), (child, []))[1].append((module, h_e))
             for child, items in by_child.values():
-                done = self.dist.quantize_independent(child, items)
+                if self.dist is not None:
+                    done = self.dist.quantize_independent(child, items)
+                else:
+                    done = child.quantize_independent(items)
                 for module, _h in items:
                     name = qz.module_to_name[module]
                     if child is not qz:

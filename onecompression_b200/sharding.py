@@ -194,30 +194,20 @@ class ShardedContext:
         from . import kernels
         from .quantizer.gptq._gptq import GPTQ, GPTQResult
 
-        if compute is None:
-            def compute(weight, hessian):
-                factor = kernels.factor_hessian(hessian, quantizer.percdamp, quantizer.actorder)
-                out = kernels.gptq_quantize(weight, factor, wbits=bits, groupsize=gs, sym=quantizer.sym,
-                                            blocksize=quantizer.blocksize, pack=True, mse=bool(quantizer.mse),
-                                            q_grid=quantizer.q_grid, q_norm=quantizer.q_norm)
-                if quantizer.actorder:
-                    out["perm"] = factor.perm.to(torch.int64)
-                return out
-
         results = {}
         local = {}
         t_local = {}
-        for i, (module, hessian) in enumerate(items):
-            if i % self.world != self.rank:
-                continue
-            name = quantizer.module_to_name[module]
-            bits = GPTQ.resolve_bits(name, quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
-            gs = GPTQ.resolve_groupsize(name, quantizer.groupsize, quantizer.mlp_groupsize)
-            t0 = time.time()
-            local[i] = compute(module.weight.data, hessian)
-            if module.weight.is_cuda:
-                torch.cuda.synchronize(module.weight.device)
-            t_local[i] = time.time() - t0
+        mine = [(i, item) for i, item in enumerate(items) if i % self.world == self.rank]
+        if compute is None:
+            # this rank's layers, several at a time on separate streams
+            outs = quantizer.independent_on_device([item for _i, item in mine])
+            for (i, _item), out in zip(mine, outs):
+                local[i], t_local[i] = out, out["seconds"]
+        else:
+            for i, (module, hessian) in mine:
+                t0 = time.time()
+                local[i] = compute(module.weight.data, hessian)
+                t_local[i] = time.time() - t0
         for i, (module, _h) in enumerate(items):
             owner = i % self.world
             name = quantizer.module_to_name[module]

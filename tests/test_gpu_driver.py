@@ -708,3 +708,69 @@ def test_gpt_oss_layer_unfused_bf16_through_the_driver():
     assert total > 0 and matched / total >= 0.99, matched / total
     for m, name in q.module_to_name.items():
         assert m.weight.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("act,pack,bits", [(False, True, 4), (True, True, 3), (False, False, 5)])
+def test_independent_layers_on_streams_match_serial(act, pack, bits):
+    """Experts quantized several at a time on separate streams: bit-identical to one-by-one calls."""
+    from onecompression_b200 import GPTQ, kernels
+
+    g = torch.Generator().manual_seed(17)
+    d, out, n_exp = 384, 256, 7
+    mods, hs = [], []
+    for e in range(n_exp):
+        lin = torch.nn.Linear(d, out, bias=False).half()
+        lin.weight.data = (torch.randn(out, d, generator=g) * 0.02).half()
+        lin = lin.to(DEV)
+        x = torch.randn(300 + 200 * e, d, generator=g)
+        x[:, e] *= 8
+        h, _ = kernels.hessian_from_activations(x.half().to(DEV))
+        mods.append(lin)
+        hs.append(h)
+    q1 = GPTQ(wbits=bits, groupsize=64, sym=False, actorder=act, bitpack_on_quantize=pack)
+    q2 = GPTQ(wbits=bits, groupsize=64, sym=False, actorder=act, bitpack_on_quantize=pack)
+    for e, m in enumerate(mods):
+        q1.module_to_name[m] = q2.module_to_name[m] = f"expert{e}"
+    serial = {m: q1.quantize_layer(m, None, hessian=h) for m, h in zip(mods, hs)}
+    together = q2.quantize_independent(list(zip(mods, hs)), lanes=3)
+    assert list(together) == mods
+    for m in mods:
+        a, b = serial[m], together[m]
+        for f in ("qweight", "qzeros", "scales"):
+            assert torch.equal(getattr(a, f), getattr(b, f)), f
+        assert (a.perm is None and b.perm is None) or torch.equal(a.perm, b.perm)
+        assert torch.equal(a.__dict__["_device_dequantized"], b.__dict__["_device_dequantized"])
+        assert b.quantization_time > 0 and b.qweight_original_shape == (out, d)
+
+
+def test_moe_block_with_concurrent_experts_matches_serial_path():
+    """The driver's expert branch: plain GPTQ (experts on streams) against a subclass that hooks the
+    per-layer call and therefore gets the serial path; identical results and activations."""
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
+
+    class Rec(_Recorder, GPTQ):
+        pass
+
+    outs = []
+    for cls in (Rec, GPTQ):
+        torch.manual_seed(0)
+        blk = _TinyMoEBlock(64, 128, 4).half().to(DEV)
+        for p in blk.parameters():
+            p.data.normal_(0, 0.05)
+        gen = torch.Generator(device=DEV).manual_seed(9)
+        x0 = torch.randn(48, 64, 64, device=DEV, generator=gen).half()
+        q = cls(wbits=4, groupsize=32, sym=False, exclude_layer_keywords=["router"])
+        q.seen, q.inputs = [], {}
+        for n, m in blk.named_modules():
+            if isinstance(m, torch.nn.Linear) and "router" not in n:
+                q.module_to_name[m] = f"model.layers.0.{n}"
+        nq, _ = BlockQuantizer(q, QEPConfig(device=DEV), batch_size=16, device=DEV).run(blk, x0.clone(), x0.clone(), {})
+        outs.append((q.results, nq))
+    assert set(outs[0][0]) == set(outs[1][0])
+    for name, r in outs[0][0].items():
+        s = outs[1][0][name]
+        assert r.qweight_is_packed == s.qweight_is_packed
+        for f in ("qweight", "qzeros", "scales"):
+            assert torch.equal(getattr(r, f), getattr(s, f)), (name, f)
+    assert torch.equal(outs[0][1], outs[1][1])
