@@ -171,6 +171,20 @@ int oc_qep_adjust(void* W, long long ldw, int out, int d, const float* C, long l
                   const float* U, long long ldu, const int* perm, const unsigned char* dead,
                   float perccorr, int w_dtype, void* workspace, long long workspace_bytes, void* stream);
 
+/* The same column loop for `batch` problems of equal shape, e.g. the experts of a mixture, each
+ * with its own factor: every array holds the problems one after another (W [batch, out, ldw],
+ * U [batch, d, ldu], perm / invperm / dead [batch, d], qweight [batch, d*bits/32, out], qzeros
+ * [batch, G, out*bits/32], scales / zeros [batch, G, out], codes [batch, out, d], w_hat
+ * [batch, out, d]); the workspace is batch times oc_gptq_workspace_bytes.  One chain of launches
+ * serves all problems (the reference quantizes them one after another,
+ * onecomp/qep/_quantize_with_qep_arch.py:546-613). */
+int oc_gptq_quantize_batched(int batch, const void* W, long long ldw, int out, int d, const float* U,
+                             long long ldu, const int* perm, const int* invperm, const unsigned char* dead,
+                             int wbits, int groupsize, int sym, int blocksize, int mse, int q_grid,
+                             float q_norm, int sm_count, int* qweight, int* qzeros, void* scales16,
+                             float* scales32, int* zeros, int* codes, void* w_hat, int w_dtype,
+                             void* workspace, long long workspace_bytes, void* stream);
+
 /* ---- block passes of the QEP driver ----------------------------------------------------
  * y = weight * fp16( float(x) * rsqrt(mean(float(x)^2) + eps) ) for x, y [rows, d] fp16 and
  * weight [d] fp16: the RMSNorm of Llama / Mistral / Qwen blocks in one kernel.  The reference's

@@ -31,6 +31,9 @@ struct ColArgs {
   float* scales; float* zeros;  // [G][out] fp32 (G = 1 for per-channel)
   int gs, maxq, sym;
   int mse_steps; float mse_grid, mse_norm;   // mse_steps = 0: plain min/max fit
+  // batched problems (blockIdx.y): element strides between consecutive problems, 0 for one problem
+  long long sW, sU, sE, sC, sS;
+  int batch;
 };
 
 // scale / zero over the values v[0..n), reference: GPTQExcecutor.find_params
@@ -104,6 +107,11 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
   const int tid = threadIdx.x;
   const int row0 = blockIdx.x * NROWS;
   const int count = a.count, i1 = a.i1;
+  {
+    const long long b = blockIdx.y;      // problem of a batch
+    a.Wf += b * a.sW; a.U += b * a.sU; a.ErrT += b * a.sE; a.codesT += b * a.sC;
+    a.scales += b * a.sS; a.zeros += b * a.sS;
+  }
 
   for (int e = tid; e < BLK * BLK; e += LOADERS) {
     const int i = e / BLK, j = e % BLK;
@@ -200,8 +208,16 @@ __global__ void gptq_prepare_kernel(const void* __restrict__ W, int bf16, long l
                                     const int* __restrict__ perm, const unsigned char* __restrict__ dead,
                                     float* __restrict__ Wf, long long ldw, int per_channel, int maxq,
                                     int sym, int mse_steps, float mse_grid, float mse_norm,
-                                    float* __restrict__ scales, float* __restrict__ zeros) {
+                                    float* __restrict__ scales, float* __restrict__ zeros,
+                                    long long s_win, long long s_wf, long long s_par) {
   const int row = blockIdx.x;
+  {
+    const long long b = blockIdx.y;      // problem of a batch
+    W = static_cast<const char*>(W) + b * s_win * 2;
+    Wf += b * s_wf; scales += b * s_par; zeros += b * s_par;
+    if (perm) perm += b * d;
+    if (dead) dead += b * d;
+  }
   const long long src0 = (long long)row * ldw_in;
   float* dst = Wf + (long long)row * ldw;
   float mn = 0.f, mx = 0.f;
@@ -380,7 +396,7 @@ int launch_block_t(const ColArgs& a, cudaStream_t stream) {
     OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS, ALIGNED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  gptq_block_kernel<WARPS, ALIGNED><<<oc_div_up(a.out, WARPS * 32), LOADERS, smem, stream>>>(a);
+  gptq_block_kernel<WARPS, ALIGNED><<<dim3(oc_div_up(a.out, WARPS * 32), a.batch), LOADERS, smem, stream>>>(a);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }
@@ -407,22 +423,21 @@ extern "C" long long oc_gptq_workspace_bytes(int out, int d, int groupsize) {
   return b + 256;
 }
 
-// See include/onecomp_b200.h for the contract.
-extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d, const float* U,
-                                long long ldu, const int* perm, const int* invperm,
-                                const unsigned char* dead, int wbits, int groupsize, int sym,
-                                int blocksize, int mse, int q_grid, float q_norm, int sm_count,
-                                int* qweight, int* qzeros, void* scales16_,
-                                float* scales32, int* zeros_i32, long long ld_out, int* codes,
-                                void* what_, long long ldwh, int w_dtype, void* workspace,
-                                long long workspace_bytes, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  const void* W = W_;
-  __half* scales16 = (__half*)scales16_;
-  void* what = what_;
+// The column loop for `batch` problems of equal shape laid out one after another (every array of
+// problem b starts b times its per-problem size after problem 0).  One chain of launches serves
+// all problems: the block kernel and the preparation take the problem from blockIdx.y, the
+// trailing updates are batched products.
+static int gptq_quantize_impl(int batch, const void* W, long long ldw_in, int out, int d, const float* U,
+                              long long ldu, const int* perm, const int* invperm, const unsigned char* dead,
+                              int wbits, int groupsize, int sym, int blocksize, int mse, int q_grid,
+                              float q_norm, int sm_count, int* qweight, int* qzeros, __half* scales16,
+                              float* scales32, int* zeros_i32, long long ld_out, int* codes, void* what,
+                              long long ldwh, int w_dtype, void* workspace, long long workspace_bytes,
+                              cudaStream_t stream) {
   OC_REQUIRE(w_dtype == OC_DTYPE_F16 || w_dtype == OC_DTYPE_BF16, "gptq_quantize: unknown weight dtype");
   const int bf16 = w_dtype == OC_DTYPE_BF16;
   OC_REQUIRE(W && U && workspace, "gptq_quantize: null pointer");
+  OC_REQUIRE(batch >= 1 && batch <= 65535, "gptq_quantize: batch must be in 1..65535");
   OC_REQUIRE(out > 0 && d > 0 && ldw_in >= d && ldu >= d, "gptq_quantize: bad dimensions");
   OC_REQUIRE(wbits >= 1 && wbits <= 15, "gptq_quantize: wbits must be in 1..15");
   OC_REQUIRE(groupsize == -1 || groupsize >= 1, "gptq_quantize: groupsize must be -1 or >= 1");
@@ -436,30 +451,35 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
     if (qweight) OC_REQUIRE(d % f == 0, "gptq_quantize: in_features not divisible by the pack factor");
     if (qzeros) OC_REQUIRE(out % f == 0 && ld_out % f == 0, "gptq_quantize: out_features not divisible by the pack factor");
   }
-  if (workspace_bytes < oc_gptq_workspace_bytes(out, d, groupsize)) {
+  const long long ws_one = oc_gptq_workspace_bytes(out, d, groupsize);
+  if (workspace_bytes < ws_one * batch) {
     oc_set_last_error("gptq_quantize: workspace too small");
     return OC_ERR_WORKSPACE;
   }
   if (ld_out < out) ld_out = out;
   const int G = (groupsize == -1) ? 1 : (d + groupsize - 1) / groupsize;
   const long long ldw = round4(d), lde = round4(out);
+  // workspace: all problems' Wf, then all ErrT, codesT, scales, zeros (each contiguous over the batch)
+  const long long nWf = (long long)out * ldw, nErr = (long long)SUPER * BLK * lde;
+  const long long nCodes = round4((long long)d * out * 2) / 2, nPar = (long long)G * out;
   char* ws = (char*)workspace;
-  float* Wf = (float*)ws;                      ws += (long long)out * ldw * 4;
-  float* ErrT = (float*)ws;                    ws += (long long)SUPER * BLK * lde * 4;
-  unsigned short* codesT = (unsigned short*)ws; ws += round4((long long)d * out * 2);
-  float* scales = (float*)ws;                  ws += (long long)G * out * 4;
+  float* Wf = (float*)ws;                       ws += nWf * 4 * batch;
+  float* ErrT = (float*)ws;                     ws += nErr * 4 * batch;
+  unsigned short* codesT = (unsigned short*)ws; ws += nCodes * 2 * batch;
+  float* scales = (float*)ws;                   ws += nPar * 4 * batch;
   float* zeros = (float*)ws;
   const int maxq = (1 << wbits) - 1;
+  const long long sU = (long long)d * ldu, sWin = (long long)out * ldw_in;
 
   OC_REQUIRE(!mse || (q_grid >= 1 && q_norm > 0.f), "gptq_quantize: mse needs q_grid >= 1 and q_norm > 0");
   const int mse_steps = mse ? (int)(0.8 * q_grid) : 0;   // maxshrink = 0.8 as in the reference
-  gptq_prepare_kernel<<<out, 256, 0, stream>>>(W, bf16, ldw_in, out, d, perm, dead, Wf, ldw,
-                                               groupsize == -1 ? 1 : 0, maxq, sym, mse_steps,
-                                               (float)q_grid, q_norm, scales, zeros);
+  gptq_prepare_kernel<<<dim3(out, batch), 256, 0, stream>>>(W, bf16, ldw_in, out, d, perm, dead, Wf, ldw,
+                                                            groupsize == -1 ? 1 : 0, maxq, sym, mse_steps,
+                                                            (float)q_grid, q_norm, scales, zeros, sWin, nWf, nPar);
   OC_CHECK_LAUNCH();
 
   if (sm_count <= 0) sm_count = 148;
-  const int warps_total = oc_div_up(out, 32);
+  const int warps_total = oc_div_up(out, 32) * batch;
   const int per_sm = oc_div_up(warps_total, sm_count);
   // The lazy-batch update is done at two distances.  After each block the columns up to the
   // end of its group of SUPER blocks are updated at once (they are needed next); the columns
@@ -476,7 +496,7 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
     const int s1 = min(d, s0 + super_cols);                 // one past its last column
     float* err_rows = ErrT + (long long)(i1 - s0) * lde;
     ColArgs a{Wf, ldw, out, d, i1, count, U, ldu, err_rows, lde, codesT, scales, zeros, groupsize, maxq, sym,
-              mse_steps, (float)q_grid, q_norm};
+              mse_steps, (float)q_grid, q_norm, nWf, sU, nErr, nCodes, nPar, batch};
     int rc;
     if (per_sm <= 1) rc = launch_block<1>(a, stream);
     else if (per_sm <= 2) rc = launch_block<2>(a, stream);
@@ -486,7 +506,8 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
     const int i2 = i1 + count;
     OcGemm g{};
     g.lda = lde; g.transA = 1; g.ldb = ldu; g.transB = 0; g.ldc = ldw;
-    g.M = out; g.alpha = -1.f; g.beta = 1.f; g.flags = 0; g.batch = 1;
+    g.M = out; g.alpha = -1.f; g.beta = 1.f; g.flags = 0;
+    g.batch = batch; g.strideA = nErr; g.strideB = sU; g.strideC = nWf;
     if (i2 < s1) {
       g.A = err_rows; g.K = count;
       g.B = U + (long long)i1 * ldu + i2; g.C = Wf + i2; g.N = s1 - i2;
@@ -501,25 +522,65 @@ extern "C" int oc_gptq_quantize(const void* W_, long long ldw_in, int out, int d
   }
 
   const int tb = 128;
-  if (qweight) {
-    const int prow = (wbits == 3) ? d / 32 : d / (32 / wbits);
-    pack_qweight_kernel<<<dim3(oc_div_up(out, tb), prow), tb, 0, stream>>>(codesT, out, d, invperm, wbits, qweight, ld_out);
-    OC_CHECK_LAUNCH();
-  }
-  if (qzeros) {
-    const int f = (wbits == 3) ? 32 : 32 / wbits;
-    const long long ldz = (wbits == 3) ? ld_out / 32 * 3 : ld_out / f;
-    pack_qzeros_kernel<<<dim3(oc_div_up(out / f, tb), G), tb, 0, stream>>>(zeros, out, G, wbits, qzeros, ldz);
-    OC_CHECK_LAUNCH();
-  }
-  if (scales16 || scales32 || zeros_i32) {
-    cast_params_kernel<<<dim3(oc_div_up(out, tb), G), tb, 0, stream>>>(scales, zeros, out, G, scales16, ld_out, scales32, zeros_i32);
-    OC_CHECK_LAUNCH();
-  }
-  if (codes || what) {
-    unpermute_outputs_kernel<<<dim3(oc_div_up(d, 32), oc_div_up(out, 32)), dim3(32, 8), 0, stream>>>(
-        codesT, out, d, invperm, groupsize, scales, zeros, codes, d, what, ldwh, bf16);
-    OC_CHECK_LAUNCH();
+  const int f = (wbits == 3) ? 32 : ((wbits == 2 || wbits == 4 || wbits == 8) ? 32 / wbits : 1);
+  const long long ldz = (wbits == 3) ? ld_out / 32 * 3 : ld_out / f;
+  const long long prow = (wbits == 3) ? d / 32 * 3 : d / f;     // rows of one problem's packed weight
+  for (int b = 0; b < batch; ++b) {
+    const unsigned short* cT = codesT + b * nCodes;
+    const float* sc = scales + b * nPar;
+    const float* zr = zeros + b * nPar;
+    const int* ip = invperm ? invperm + (long long)b * d : nullptr;
+    if (qweight) {
+      const int prow_k = (wbits == 3) ? d / 32 : d / (32 / wbits);
+      pack_qweight_kernel<<<dim3(oc_div_up(out, tb), prow_k), tb, 0, stream>>>(cT, out, d, ip, wbits,
+                                                                               qweight + b * prow * ld_out, ld_out);
+      OC_CHECK_LAUNCH();
+    }
+    if (qzeros) {
+      pack_qzeros_kernel<<<dim3(oc_div_up(out / f, tb), G), tb, 0, stream>>>(zr, out, G, wbits,
+                                                                             qzeros + b * G * ldz, ldz);
+      OC_CHECK_LAUNCH();
+    }
+    if (scales16 || scales32 || zeros_i32) {
+      cast_params_kernel<<<dim3(oc_div_up(out, tb), G), tb, 0, stream>>>(
+          sc, zr, out, G, scales16 ? scales16 + b * G * ld_out : nullptr, ld_out,
+          scales32 ? scales32 + b * G * ld_out : nullptr, zeros_i32 ? zeros_i32 + b * G * ld_out : nullptr);
+      OC_CHECK_LAUNCH();
+    }
+    if (codes || what) {
+      void* wh = what ? (void*)((char*)what + (long long)b * out * ldwh * 2) : nullptr;
+      unpermute_outputs_kernel<<<dim3(oc_div_up(d, 32), oc_div_up(out, 32)), dim3(32, 8), 0, stream>>>(
+          cT, out, d, ip, groupsize, sc, zr, codes ? codes + (long long)b * out * d : nullptr, d, wh, ldwh, bf16);
+      OC_CHECK_LAUNCH();
+    }
   }
   return OC_OK;
+}
+
+// See include/onecomp_b200.h for the contracts.
+extern "C" int oc_gptq_quantize(const void* W, long long ldw_in, int out, int d, const float* U,
+                                long long ldu, const int* perm, const int* invperm,
+                                const unsigned char* dead, int wbits, int groupsize, int sym,
+                                int blocksize, int mse, int q_grid, float q_norm, int sm_count,
+                                int* qweight, int* qzeros, void* scales16,
+                                float* scales32, int* zeros_i32, long long ld_out, int* codes,
+                                void* what, long long ldwh, int w_dtype, void* workspace,
+                                long long workspace_bytes, void* stream) {
+  return gptq_quantize_impl(1, W, ldw_in, out, d, U, ldu, perm, invperm, dead, wbits, groupsize, sym, blocksize,
+                            mse, q_grid, q_norm, sm_count, qweight, qzeros, (__half*)scales16, scales32,
+                            zeros_i32, ld_out, codes, what, ldwh, w_dtype, workspace, workspace_bytes,
+                            (cudaStream_t)stream);
+}
+
+extern "C" int oc_gptq_quantize_batched(int batch, const void* W, long long ldw_in, int out, int d,
+                                        const float* U, long long ldu, const int* perm, const int* invperm,
+                                        const unsigned char* dead, int wbits, int groupsize, int sym,
+                                        int blocksize, int mse, int q_grid, float q_norm, int sm_count,
+                                        int* qweight, int* qzeros, void* scales16, float* scales32,
+                                        int* zeros_i32, int* codes, void* what, int w_dtype, void* workspace,
+                                        long long workspace_bytes, void* stream) {
+  return gptq_quantize_impl(batch, W, ldw_in, out, d, U, ldu, perm, invperm, dead, wbits, groupsize, sym,
+                            blocksize, mse, q_grid, q_norm, sm_count, qweight, qzeros, (__half*)scales16,
+                            scales32, zeros_i32, out, codes, what, d, w_dtype, workspace, workspace_bytes,
+                            (cudaStream_t)stream);
 }

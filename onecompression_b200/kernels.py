@@ -237,7 +237,7 @@ def factor_hessian(h: torch.Tensor, percdamp: float, actorder: bool, max_retries
     )
 
 
-def factor_hessian_launch(h: torch.Tensor, percdamp: float, actorder: bool) -> dict:
+def factor_hessian_launch(h: torch.Tensor, percdamp: float, actorder: bool, buffers: Optional[dict] = None) -> dict:
     """First attempt of ``factor_hessian`` enqueued on the current stream without waiting for its
     status: lets several small factorisations run side by side on different streams.  Finish
     with ``factor_hessian_resolve``."""
@@ -248,11 +248,12 @@ def factor_hessian_launch(h: torch.Tensor, percdamp: float, actorder: bool) -> d
         h = h.contiguous()
     d = h.shape[0]
     dev = h.device
+    buffers = buffers or {}       # contiguous views to write into (e.g. slices of batched arrays)
     out = {
-        "h": h, "u": torch.empty((d, d), dtype=torch.float32, device=dev),
-        "perm": torch.empty(d, dtype=torch.int32, device=dev),
-        "invperm": torch.empty(d, dtype=torch.int32, device=dev),
-        "dead": torch.empty(d, dtype=torch.uint8, device=dev),
+        "h": h, "u": buffers.get("u", None) if buffers.get("u", None) is not None else torch.empty((d, d), dtype=torch.float32, device=dev),
+        "perm": buffers["perm"] if "perm" in buffers else torch.empty(d, dtype=torch.int32, device=dev),
+        "invperm": buffers["invperm"] if "invperm" in buffers else torch.empty(d, dtype=torch.int32, device=dev),
+        "dead": buffers["dead"] if "dead" in buffers else torch.empty(d, dtype=torch.uint8, device=dev),
         "damp": torch.empty(2, dtype=torch.float32, device=dev),
         "status": torch.empty(1, dtype=torch.int32, device=dev),
         "percdamp": float(percdamp), "actorder": bool(actorder),
@@ -362,6 +363,46 @@ def gptq_quantize(
             deq.stride(0) if deq is not None else d, _DTYPES[weight.dtype], ptr(ws), ws.numel(), stream_handle(),
         )
     return outputs
+
+
+def gptq_quantize_batched(weights: torch.Tensor, u: torch.Tensor, dead: torch.Tensor, wbits: int,
+                          groupsize: int, sym: bool, perm: Optional[torch.Tensor] = None,
+                          invperm: Optional[torch.Tensor] = None, blocksize: int = 128, pack: bool = True,
+                          mse: bool = False, q_grid: int = 600, q_norm: float = 2.4):
+    """The column loop for a batch of equally shaped problems, each with its own factor: ``weights``
+    [B, out, d] fp16 / bf16, ``u`` [B, d, d] fp32, ``dead`` [B, d] uint8, for act-order ``perm`` and
+    ``invperm`` [B, d] int32.  One chain of launches for all problems.  Returns a dict of batched
+    outputs: qweight / qzeros (packed) or codes / zeros, scales (fp16 [B, G, out]), dequantized
+    [B, out, d]."""
+    _require_cuda(weights, "weights")
+    if weights.dtype not in _DTYPES or weights.dim() != 3 or not weights.is_contiguous():
+        raise TypeError("gptq_quantize_batched expects a contiguous [B, out, d] fp16 or bf16 tensor")
+    batch, out, d = weights.shape
+    dev = weights.device
+    if u.shape != (batch, d, d) or u.dtype != torch.float32 or not u.is_contiguous():
+        raise ValueError("u must be a contiguous fp32 [B, d, d] tensor")
+    groups = 1 if groupsize == -1 else (d + groupsize - 1) // groupsize
+    res = {"scales": torch.empty((batch, groups, out), dtype=torch.float16, device=dev),
+           "zeros": torch.empty((batch, groups, out), dtype=torch.int32, device=dev),
+           "dequantized": torch.empty((batch, out, d), dtype=weights.dtype, device=dev)}
+    if pack:
+        if wbits not in PACKABLE_WBITS:
+            raise ValueError(f"packing supports wbits in {PACKABLE_WBITS}; got {wbits}")
+        f = 32 if wbits == 3 else 32 // wbits
+        assert d % f == 0 and out % f == 0, "shapes must be divisible by the pack factor"
+        res["qweight"] = torch.empty((batch, d * wbits // 32, out), dtype=torch.int32, device=dev)
+        res["qzeros"] = torch.empty((batch, groups, out * wbits // 32), dtype=torch.int32, device=dev)
+    else:
+        res["codes"] = torch.empty((batch, out, d), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        nbytes = _lib.load().oc_gptq_workspace_bytes(out, d, groupsize) * batch
+        ws = _workspace(nbytes, dev)
+        call("oc_gptq_quantize_batched", batch, ptr(weights), d, out, d, ptr(u), d, ptr(perm), ptr(invperm),
+             ptr(dead), wbits, groupsize, 1 if sym else 0, blocksize, 1 if mse else 0, int(q_grid), float(q_norm),
+             sm_count(dev), ptr(res.get("qweight")), ptr(res.get("qzeros")), ptr(res["scales"]), None,
+             ptr(res["zeros"]), ptr(res.get("codes")), ptr(res["dequantized"]), _DTYPES[weights.dtype], ptr(ws),
+             ws.numel(), stream_handle())
+    return res
 
 
 # ---------------------------------------------------------------------------

@@ -380,69 +380,71 @@ class GPTQ(Quantizer):
 
     # ------------------------------------------------------------------ many small layers, own Hessians
 
-    def independent_on_device(self, items, lanes: int = 1):
+    def independent_on_device(self, items):
         """Factor and quantize layers that each come with a Hessian of their own (``items`` =
-        [(module, hessian)], no weight correction) with one device synchronisation for all of them.
-        ``lanes`` > 1 spreads them over that many CUDA streams; on B200 this does not pay (32 experts
-        of 2880 x 2880: 270 ms on one stream, 277 ms on two, 500 ms on four), because the
-        factorisation and trailing-update kernels each claim whole SMs (shared memory, TMEM) and
-        chains from different streams mostly queue behind one another.  Returns, in order, dicts with the device outputs of
-        ``kernels.gptq_quantize`` plus ``perm`` (int64 or None), ``bits``, ``gs``, ``seconds``;
-        everything is complete (device-synchronised) on return."""
+        [(module, hessian)], no weight correction).  Layers of equal shape and settings are batched:
+        their factors are written into one array and one chain of column-loop launches serves all of
+        them (``kernels.gptq_quantize_batched``), with a single device synchronisation for the
+        statuses of the factorisations.  Returns, in the order of ``items``, dicts with the device
+        outputs (qweight / qzeros or codes / zeros, scales, dequantized) plus ``perm`` (int64 or
+        None), ``bits``, ``gs``, ``seconds``; everything is complete on return."""
         if not items:
             return []
         dev = items[0][0].weight.device
-        main = torch.cuda.current_stream(dev)
-        streams = [torch.cuda.Stream(dev) for _ in range(max(1, min(lanes, len(items))))]
-        for st in streams:
-            st.wait_stream(main)
-        done = []
-        for w0 in range(0, len(items), len(streams)):
-            wave = items[w0:w0 + len(streams)]
-            pending, starts = [], []
-            for st, (_module, hessian) in zip(streams, wave):
-                with torch.cuda.stream(st):
-                    ev = torch.cuda.Event(enable_timing=True)
-                    ev.record()
-                    starts.append(ev)
-                    pending.append(kernels.factor_hessian_launch(hessian.to(dev), self.percdamp, self.actorder))
-            for st, (module, _h), pend, ev0 in zip(streams, wave, pending, starts):
-                name = self.module_to_name.get(module)
-                bits = GPTQ.resolve_bits(name, self.wbits, self.mlp_wbits, self.module_wbits)
-                gs = GPTQ.resolve_groupsize(name, self.groupsize, self.mlp_groupsize)
-                packed = self.bitpack_on_quantize
-                if packed and not is_packable_wbits(bits):
-                    raise ValueError(
-                        f"bitpack_on_quantize=True supports only wbits in {tuple(sorted(PACKABLE_WBITS))}; "
-                        f"got {bits}. Use bitpack_on_quantize=False for unpacked GPTQ results.")
-                with torch.cuda.stream(st):
-                    factor = kernels.factor_hessian_resolve(pend)
-                    out = kernels.gptq_quantize(
-                        _weight_matrix(module), factor, wbits=bits, groupsize=gs, sym=self.sym,
-                        blocksize=self.blocksize, pack=packed, want_codes=not packed, want_dequantized=True,
-                        mse=bool(self.mse), q_grid=self.q_grid, q_norm=self.q_norm)
-                    out["perm"] = factor.perm.to(torch.int64) if self.actorder else None
-                    ev1 = torch.cuda.Event(enable_timing=True)
-                    ev1.record()
-                for t in out.values():
-                    if isinstance(t, torch.Tensor):
-                        t.record_stream(main)
-                out.update(bits=bits, gs=gs, _timing=(ev0, ev1))
-                done.append(out)
-        for st in streams:
-            main.wait_stream(st)
-        torch.cuda.synchronize(dev)
-        for out in done:
-            ev0, ev1 = out.pop("_timing")
-            out["seconds"] = ev0.elapsed_time(ev1) / 1e3
+        packed = self.bitpack_on_quantize
+        groups = {}
+        for idx, (module, _h) in enumerate(items):
+            name = self.module_to_name.get(module)
+            bits = GPTQ.resolve_bits(name, self.wbits, self.mlp_wbits, self.module_wbits)
+            gs = GPTQ.resolve_groupsize(name, self.groupsize, self.mlp_groupsize)
+            if packed and not is_packable_wbits(bits):
+                raise ValueError(
+                    f"bitpack_on_quantize=True supports only wbits in {tuple(sorted(PACKABLE_WBITS))}; "
+                    f"got {bits}. Use bitpack_on_quantize=False for unpacked GPTQ results.")
+            w = _weight_matrix(module)
+            groups.setdefault((tuple(w.shape), w.dtype, bits, gs), []).append(idx)
+        done = [None] * len(items)
+        for (shape, _dtype, bits, gs), idxs in groups.items():
+            out_features, d = shape
+            batch = len(idxs)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            weights = torch.stack([_weight_matrix(items[i][0]) for i in idxs]).contiguous()
+            u = torch.empty((batch, d, d), dtype=torch.float32, device=dev)
+            perm = torch.empty((batch, d), dtype=torch.int32, device=dev)
+            invperm = torch.empty((batch, d), dtype=torch.int32, device=dev)
+            dead = torch.empty((batch, d), dtype=torch.uint8, device=dev)
+            pending = [kernels.factor_hessian_launch(
+                items[i][1].to(dev), self.percdamp, self.actorder,
+                buffers={"u": u[b], "perm": perm[b], "invperm": invperm[b], "dead": dead[b]})
+                for b, i in enumerate(idxs)]
+            status = torch.cat([p["status"] for p in pending]).cpu()       # the one synchronisation
+            for b in torch.nonzero(status).flatten().tolist():
+                fac = kernels.factor_hessian(pending[b]["h"], self.percdamp, self.actorder)   # retry rule
+                u[b].copy_(fac.u)
+                perm[b].copy_(fac.perm)
+                invperm[b].copy_(fac.invperm)
+                dead[b].copy_(fac.dead)
+            out = kernels.gptq_quantize_batched(
+                weights, u, dead, bits, gs, self.sym, perm if self.actorder else None,
+                invperm if self.actorder else None, blocksize=self.blocksize, pack=packed, mse=bool(self.mse),
+                q_grid=self.q_grid, q_norm=self.q_norm)
+            ev1.record()
+            torch.cuda.synchronize(dev)
+            seconds = ev0.elapsed_time(ev1) / 1e3 / batch
+            for b, i in enumerate(idxs):
+                one = {k: v[b] for k, v in out.items()}
+                one.update(perm=perm[b].to(torch.int64) if self.actorder else None, bits=bits, gs=gs,
+                           seconds=seconds)
+                done[i] = one
         return done
 
-    def quantize_independent(self, items, lanes: int = 1):
+    def quantize_independent(self, items):
         """``independent_on_device`` plus the results: {module: GPTQResult} with CPU tensors, the
         propagated weight left on the device, per-layer ``quantization_time``."""
         results = {}
         packed = self.bitpack_on_quantize
-        for (module, _h), out in zip(items, self.independent_on_device(items, lanes)):
+        for (module, _h), out in zip(items, self.independent_on_device(items)):
             out_features, in_features = module.weight.shape[0], module.weight.numel() // module.weight.shape[0]
             host = kernels.to_host([out["qweight"] if packed else out["codes"],
                                     out["qzeros"] if packed else out["zeros"], out["scales"], out["perm"]])

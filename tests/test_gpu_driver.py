@@ -711,8 +711,9 @@ def test_gpt_oss_layer_unfused_bf16_through_the_driver():
 
 
 @pytest.mark.parametrize("act,pack,bits", [(False, True, 4), (True, True, 3), (False, False, 5)])
-def test_independent_layers_on_streams_match_serial(act, pack, bits):
-    """Experts quantized several at a time on separate streams: bit-identical to one-by-one calls."""
+def test_independent_layers_batched_match_serial(act, pack, bits):
+    """Experts quantized as one batch (one chain of column-loop launches for all of them):
+    bit-identical to one-by-one calls."""
     from onecompression_b200 import GPTQ, kernels
 
     g = torch.Generator().manual_seed(17)
@@ -732,7 +733,7 @@ def test_independent_layers_on_streams_match_serial(act, pack, bits):
     for e, m in enumerate(mods):
         q1.module_to_name[m] = q2.module_to_name[m] = f"expert{e}"
     serial = {m: q1.quantize_layer(m, None, hessian=h) for m, h in zip(mods, hs)}
-    together = q2.quantize_independent(list(zip(mods, hs)), lanes=3)
+    together = q2.quantize_independent(list(zip(mods, hs)))
     assert list(together) == mods
     for m in mods:
         a, b = serial[m], together[m]
@@ -743,8 +744,8 @@ def test_independent_layers_on_streams_match_serial(act, pack, bits):
         assert b.quantization_time > 0 and b.qweight_original_shape == (out, d)
 
 
-def test_moe_block_with_concurrent_experts_matches_serial_path():
-    """The driver's expert branch: plain GPTQ (experts on streams) against a subclass that hooks the
+def test_moe_block_with_batched_experts_matches_serial_path():
+    """The driver's expert branch: plain GPTQ (experts batched) against a subclass that hooks the
     per-layer call and therefore gets the serial path; identical results and activations."""
     from onecompression_b200 import GPTQ, QEPConfig
     from onecompression_b200.qep._quantize_with_qep_arch import BlockQuantizer
