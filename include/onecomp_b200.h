@@ -117,6 +117,15 @@ int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float r
                    unsigned char* dead, float* damp_out, int* status, void* workspace,
                    long long workspace_bytes, void* stream);
 
+/* The same factorisation for `batch` matrices of equal size (the experts of a mixture), first
+ * attempt only (shift = percdamp * mean): H and U [batch, n, n] contiguous, perm / invperm / dead
+ * [batch, n], damp_out [batch, 2], status [batch]; the workspace is batch times
+ * oc_hinv_workspace_bytes(n).  The panel chain is walked once and every launch covers all
+ * matrices.  Problems whose status is non-zero are repeated singly with more damping. */
+int oc_hinv_factor_batched(int batch, const float* H, int n, float percdamp, int actorder, float* U,
+                           int* perm, int* invperm, unsigned char* dead, float* damp_out, int* status,
+                           void* workspace, long long workspace_bytes, void* stream);
+
 /* ---- GPTQ column loop ---------------------------------------------------------
  * Quantizes W [out, d] fp16 (ldw) given U from oc_hinv_factor.  Replaces run_gptq's
  * float conversion, per-channel fit, dead-column zeroing, act-order gather, the

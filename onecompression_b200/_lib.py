@@ -28,6 +28,7 @@ SIGNATURES = {
     "oc_gptq_workspace_bytes": (_L, [_I, _I, _I]),
     "oc_gptq_quantize": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P,
                               _P, _P, _P, _L, _P, _P, _L, _I, _P, _L, _P]),
+    "oc_hinv_factor_batched": (_I, [_I, _P, _I, _F, _I, _P, _P, _P, _P, _P, _P, _P, _L, _P]),
     "oc_gptq_quantize_batched": (_I, [_I, _P, _L, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                       _P, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P]),
     "oc_rtn_quantize": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),

@@ -19,9 +19,15 @@ constexpr int OB = 512;  // outer block of the two-level Cholesky
 
 // ---- diag statistics: dead columns, damping --------------------------------
 // diagv[j] = H[j,j] (1 where it is 0), dead[j], damp_out[0] = percdamp * mean(diagv)
+// Batched launches: block index `b` of the batch dimension selects the problem; `sH`, `sW`, ... are
+// the element strides between consecutive problems.
 __global__ void diag_stats_kernel(const float* __restrict__ H, long long ld, int n, float percdamp,
                                   float* __restrict__ diagv, unsigned char* __restrict__ dead,
-                                  float* __restrict__ damp_out) {
+                                  float* __restrict__ damp_out, long long sH, long long sW) {
+  {
+    const long long b = blockIdx.x;
+    H += b * sH; diagv += b * sW; dead += b * n; damp_out += b * 2;
+  }
   __shared__ double red[32];
   double s = 0.0;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
@@ -44,7 +50,9 @@ __global__ void diag_stats_kernel(const float* __restrict__ H, long long ld, int
 }
 
 // ---- act-order: stable descending argsort by counting ranks ---------------------
-__global__ void rank_sort_kernel(const float* __restrict__ key, int n, int* __restrict__ perm) {
+__global__ void rank_sort_kernel(const float* __restrict__ key, int n, int* __restrict__ perm, long long sW) {
+  key += (long long)blockIdx.y * sW;
+  perm += (long long)blockIdx.y * n;
   __shared__ float tile[1024];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const float ki = (i < n) ? key[i] : 0.f;
@@ -65,11 +73,13 @@ __global__ void rank_sort_kernel(const float* __restrict__ key, int n, int* __re
 
 __global__ void iota_kernel(int* __restrict__ perm, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) perm[i] = i;
+  if (i < n) perm[(long long)blockIdx.y * n + i] = i;
 }
 
 __global__ void invert_perm_kernel(const int* __restrict__ perm, int* __restrict__ inv, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  perm += (long long)blockIdx.y * n;
+  inv += (long long)blockIdx.y * n;
   if (i < n) inv[perm[i]] = i;
 }
 
@@ -77,10 +87,14 @@ __global__ void invert_perm_kernel(const int* __restrict__ perm, int* __restrict
 __global__ void build_reversed_kernel(const float* __restrict__ H, long long ldh, int n,
                                       const int* __restrict__ perm, const float* __restrict__ diagv,
                                       const float* __restrict__ damp, float rel_shift,
-                                      float* __restrict__ A, long long lda) {
+                                      float* __restrict__ A, long long lda, long long sH, long long sW) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int i = blockIdx.y;
   if (j >= n) return;
+  {
+    const long long b = blockIdx.z;
+    H += b * sH; perm += b * n; diagv += b * sW; damp += b * 2; A += b * sW;
+  }
   const int pi = perm[n - 1 - i], pj = perm[n - 1 - j];
   float v;
   if (i == j) v = diagv[pi] + rel_shift * damp[0];
@@ -90,10 +104,12 @@ __global__ void build_reversed_kernel(const float* __restrict__ H, long long ldh
 
 // ---- U = J X J (upper part), zero below the diagonal ------------------------------------
 __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx, int n,
-                                     float* __restrict__ U, long long ldu) {
+                                     float* __restrict__ U, long long ldu, long long sW, long long sU) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int i = blockIdx.y;
   if (j >= n) return;
+  X += (long long)blockIdx.z * sW;
+  U += (long long)blockIdx.z * sU;
   U[(long long)i * ldu + j] = (j >= i) ? X[(long long)(n - 1 - i) * ldx + (n - 1 - j)] : 0.f;
 }
 
@@ -111,7 +127,11 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
 // level (four levels, two small products each).
 __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
                                                          float* __restrict__ X, long long ldx,
-                                                         int k0, int nb, int* __restrict__ status) {
+                                                         int k0, int nb, int* __restrict__ status,
+                                                         long long sW) {
+  A += (long long)blockIdx.x * sW;
+  X += (long long)blockIdx.x * sW;
+  status += blockIdx.x;
   extern __shared__ __align__(16) float sm[];
   float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
   float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
@@ -270,48 +290,53 @@ __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, 
 
 }  // namespace
 
-// Workspace layout (floats): A[n*ld] | X[n*ld] | T[n*ld] | diagv[n] | damp[4];  ld = round_up(n,4)
+// Workspace layout of one problem (floats): A[n*ld] | X[n*ld] | T[n*ld] | diagv[n] | pad;
+// ld = round_up(n,4).  A batch keeps the problems' workspaces one after another.
 static long long factor_ws_floats(int n) {
   const long long ld = (n + 3) / 4 * 4;
-  return 3 * (long long)n * ld + ((n + 3) / 4 * 4) + 4;
+  return (3 * (long long)n * ld + ((n + 3) / 4 * 4) + 4 + 63) / 64 * 64;
 }
 
-extern "C" long long oc_hinv_workspace_bytes(int n) {
-  return factor_ws_floats(n) * 4 + (long long)((n + 3) / 4 * 4);  // + dead bytes
-}
+extern "C" long long oc_hinv_workspace_bytes(int n) { return factor_ws_floats(n) * 4; }
 
-// See include/onecomp_b200.h for the contract.
-extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float rel_shift,
-                              int actorder, int reuse_perm, float* U, long long ldu, int* perm,
-                              int* invperm, unsigned char* dead, float* damp_out, int* status,
-                              void* workspace, long long workspace_bytes, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+// Factorisation of `batch` matrices of equal size laid out one after another (H [batch, n, ldh],
+// U [batch, n, ldu], perm / invperm / dead [batch, n], damp_out [batch, 2], status [batch]).  The
+// panel chain is walked once; every launch covers all problems.
+static int hinv_factor_impl(int batch, const float* H, long long ldh, int n, float percdamp, float rel_shift,
+                            int actorder, int reuse_perm, float* U, long long ldu, int* perm, int* invperm,
+                            unsigned char* dead, float* damp_out, int* status, void* workspace,
+                            long long workspace_bytes, cudaStream_t stream) {
   OC_REQUIRE(H && U && perm && invperm && dead && damp_out && status && workspace, "hinv_factor: null pointer");
   OC_REQUIRE(n > 0 && ldh >= n && ldu >= n, "hinv_factor: bad dimensions");
-  if (workspace_bytes < oc_hinv_workspace_bytes(n)) {
+  OC_REQUIRE(batch >= 1 && batch <= 65535, "hinv_factor: batch must be in 1..65535");
+  const long long sW = factor_ws_floats(n);
+  if (workspace_bytes < sW * 4 * batch) {
     oc_set_last_error("hinv_factor: workspace too small");
     return OC_ERR_WORKSPACE;
   }
   const long long ld = (n + 3) / 4 * 4;
+  const long long sH = (long long)n * ldh, sU = (long long)n * ldu;
   float* A = (float*)workspace;
   float* X = A + (long long)n * ld;
   float* T = X + (long long)n * ld;
   float* diagv = T + (long long)n * ld;
 
-  OC_CUDA(cudaMemsetAsync(status, 0, sizeof(int), stream));
-  diag_stats_kernel<<<1, 1024, 0, stream>>>(H, ldh, n, percdamp, diagv, dead, damp_out);
+  OC_CUDA(cudaMemsetAsync(status, 0, sizeof(int) * batch, stream));
+  diag_stats_kernel<<<batch, 1024, 0, stream>>>(H, ldh, n, percdamp, diagv, dead, damp_out, sH, sW);
   OC_CHECK_LAUNCH();
   const int tb = 256, gb = oc_div_up(n, tb);
   if (!reuse_perm) {
-    if (actorder) rank_sort_kernel<<<gb, tb, 0, stream>>>(diagv, n, perm);
-    else iota_kernel<<<gb, tb, 0, stream>>>(perm, n);
+    if (actorder) rank_sort_kernel<<<dim3(gb, batch), tb, 0, stream>>>(diagv, n, perm, sW);
+    else iota_kernel<<<dim3(gb, batch), tb, 0, stream>>>(perm, n);
     OC_CHECK_LAUNCH();
-    invert_perm_kernel<<<gb, tb, 0, stream>>>(perm, invperm, n);
+    invert_perm_kernel<<<dim3(gb, batch), tb, 0, stream>>>(perm, invperm, n);
     OC_CHECK_LAUNCH();
   }
-  build_reversed_kernel<<<dim3(gb, n), tb, 0, stream>>>(H, ldh, n, perm, diagv, damp_out, rel_shift, A, ld);
+  build_reversed_kernel<<<dim3(gb, n, batch), tb, 0, stream>>>(H, ldh, n, perm, diagv, damp_out, rel_shift, A,
+                                                                ld, sH, sW);
   OC_CHECK_LAUNCH();
-  OC_CUDA(cudaMemsetAsync(X, 0, (size_t)n * ld * sizeof(float), stream));
+  for (int b = 0; b < batch; ++b)
+    OC_CUDA(cudaMemsetAsync(X + b * sW, 0, (size_t)n * ld * sizeof(float), stream));
 
   // ---- blocked right-looking Cholesky --------------------------------------------------
   static bool attr_set = false;
@@ -320,6 +345,7 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
     OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
+  auto batched = [&](OcGemm& g) { g.batch = batch; g.strideA = sW; g.strideB = sW; g.strideC = sW; };
   // Two levels: inside an outer block of OB columns every 128-column panel updates only the
   // rest of that outer block (full height); the matrix behind the outer block is updated once per
   // outer block with K = OB, so it is read and written n/OB times instead of n/128 times.
@@ -327,7 +353,7 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
     const int kend = min(n, K0 + OB);
     for (int k0 = K0; k0 < kend; k0 += NB) {
       const int nb = min(NB, n - k0);
-      potrf_diag_kernel<<<1, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status);
+      potrf_diag_kernel<<<batch, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status, sW);
       OC_CHECK_LAUNCH();
       const int rest = n - k0 - nb;
       if (rest <= 0) break;
@@ -336,7 +362,8 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
       // panel <- panel * (Lkk^-1)^T  (in place: one column tile, every CTA reads its rows first)
       g.A = panel; g.lda = ld; g.B = X + (long long)k0 * ld + k0; g.ldb = ld; g.C = panel; g.ldc = ld;
       g.M = rest; g.N = nb; g.K = nb; g.alpha = 1.f; g.beta = 0.f; g.transA = 0; g.transB = 1;
-      g.flags = 0; g.batch = 1;
+      g.flags = 0;
+      batched(g);
       int rc = oc_gemm_f32_launch(g, stream);
       if (rc) return rc;
       const int inner = kend - (k0 + nb);
@@ -346,7 +373,8 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
       s.A = panel; s.lda = ld; s.B = panel; s.ldb = ld;
       s.C = A + (long long)(k0 + nb) * ld + (k0 + nb); s.ldc = ld;
       s.M = rest; s.N = inner; s.K = nb; s.alpha = -1.f; s.beta = 1.f; s.transA = 0; s.transB = 1;
-      s.flags = OC_GEMM_SKIP_UPPER_TILES; s.batch = 1;
+      s.flags = OC_GEMM_SKIP_UPPER_TILES;
+      batched(s);
       rc = oc_gemm_f32_launch(s, stream);
       if (rc) return rc;
     }
@@ -358,12 +386,15 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
     t.A = P; t.lda = ld; t.B = P; t.ldb = ld;
     t.C = A + (long long)kend * ld + kend; t.ldc = ld;
     t.M = rest2; t.N = rest2; t.K = kend - K0; t.alpha = -1.f; t.beta = 1.f; t.transA = 0; t.transB = 1;
-    t.flags = OC_GEMM_SKIP_UPPER_TILES; t.batch = 1;
+    t.flags = OC_GEMM_SKIP_UPPER_TILES;
+    batched(t);
     const int rc2 = oc_gemm_f32_launch(t, stream);
     if (rc2) return rc2;
   }
 
   // ---- recursive blocked inverse of L: X holds the inverted diagonal blocks -----------------
+  // One matrix: the uniform problems of a level form one batched product.  Several matrices: the
+  // batch dimension is taken by the matrices and the problems of a level are launched one by one.
   for (long long s = NB; s < n; s *= 2) {
     const int nprob = (int)((n + 2 * s - 1) / (2 * s));
     int nfull = 0;
@@ -371,24 +402,34 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
       const long long mid = 2 * s * m + s, end = 2 * s * m + 2 * s;
       if (mid < n && end <= n) nfull = m + 1;
     }
-    for (int pass = 0; pass < 2; ++pass) {
-      // pass 0: the uniform problems as one batch; pass 1: a ragged last problem, if any
-      int first, count, rows = 0;
-      if (pass == 0) { first = 0; count = nfull; rows = (int)s; }
+    // (first problem, count as one launch, rows of the lower block)
+    struct Launch { int first, count, rows; };
+    Launch list[2 + 1];
+    int nl = 0;
+    if (batch == 1) {
+      if (nfull > 0) list[nl++] = {0, nfull, (int)s};
+      const long long mid = 2 * s * nfull + s;
+      if (nfull < nprob && mid < n) list[nl++] = {nfull, 1, (int)(n - mid)};
+    }
+    const int total = (batch == 1) ? nl : nprob;
+    for (int li = 0; li < total; ++li) {
+      int first, count, rows;
+      if (batch == 1) { first = list[li].first; count = list[li].count; rows = list[li].rows; }
       else {
-        first = nfull; count = 0;
+        first = li; count = 1;
         const long long mid = 2 * s * first + s;
-        if (first < nprob && mid < n) { count = 1; rows = (int)(n - mid); }
+        if (mid >= n) continue;
+        rows = (int)min((long long)s, n - mid);
       }
-      if (count == 0) continue;
       const long long r0 = 2 * s * first, mid = r0 + s;
-      const long long stride = 2 * s * (ld + 1);
+      const long long stride = (batch == 1) ? 2 * s * (ld + 1) : sW;
+      const int nb_launch = (batch == 1) ? count : batch;
       OcGemm g1{};  // T21 = L21 * X11   (X11 lower triangular)
       g1.A = A + mid * ld + r0; g1.lda = ld; g1.strideA = stride;
       g1.B = X + r0 * ld + r0; g1.ldb = ld; g1.strideB = stride;
       g1.C = T + mid * ld + r0; g1.ldc = ld; g1.strideC = stride;
       g1.M = rows; g1.N = (int)s; g1.K = (int)s; g1.alpha = 1.f; g1.beta = 0.f;
-      g1.flags = OC_GEMM_KLO_FROM_N; g1.batch = count;
+      g1.flags = OC_GEMM_KLO_FROM_N; g1.batch = nb_launch;
       int rc = oc_gemm_f32_launch(g1, stream);
       if (rc) return rc;
       OcGemm g2{};  // X21 = -X22 * T21  (X22 lower triangular)
@@ -396,12 +437,28 @@ extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percda
       g2.B = T + mid * ld + r0; g2.ldb = ld; g2.strideB = stride;
       g2.C = X + mid * ld + r0; g2.ldc = ld; g2.strideC = stride;
       g2.M = rows; g2.N = (int)s; g2.K = rows; g2.alpha = -1.f; g2.beta = 0.f;
-      g2.flags = OC_GEMM_KHI_FROM_M; g2.batch = count;
+      g2.flags = OC_GEMM_KHI_FROM_M; g2.batch = nb_launch;
       rc = oc_gemm_f32_launch(g2, stream);
       if (rc) return rc;
     }
   }
-  reverse_upper_kernel<<<dim3(gb, n), tb, 0, stream>>>(X, ld, n, U, ldu);
+  reverse_upper_kernel<<<dim3(gb, n, batch), tb, 0, stream>>>(X, ld, n, U, ldu, sW, sU);
   OC_CHECK_LAUNCH();
   return OC_OK;
+}
+
+// See include/onecomp_b200.h for the contracts.
+extern "C" int oc_hinv_factor(const float* H, long long ldh, int n, float percdamp, float rel_shift,
+                              int actorder, int reuse_perm, float* U, long long ldu, int* perm,
+                              int* invperm, unsigned char* dead, float* damp_out, int* status,
+                              void* workspace, long long workspace_bytes, void* stream) {
+  return hinv_factor_impl(1, H, ldh, n, percdamp, rel_shift, actorder, reuse_perm, U, ldu, perm, invperm, dead,
+                          damp_out, status, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int oc_hinv_factor_batched(int batch, const float* H, int n, float percdamp, int actorder, float* U,
+                                      int* perm, int* invperm, unsigned char* dead, float* damp_out,
+                                      int* status, void* workspace, long long workspace_bytes, void* stream) {
+  return hinv_factor_impl(batch, H, n, n, percdamp, 1.f, actorder, 0, U, n, perm, invperm, dead, damp_out,
+                          status, workspace, workspace_bytes, (cudaStream_t)stream);
 }

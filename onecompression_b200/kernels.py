@@ -237,6 +237,30 @@ def factor_hessian(h: torch.Tensor, percdamp: float, actorder: bool, max_retries
     )
 
 
+def factor_hessians_batched(hs: torch.Tensor, percdamp: float, actorder: bool) -> dict:
+    """First attempt of the factorisation for a batch of Hessians ``hs`` [B, n, n] (fp32, contiguous),
+    enqueued without waiting: dict(u [B,n,n], perm, invperm int32 [B,n], dead uint8 [B,n], damp
+    [B,2], status int32 [B]).  A non-zero status means that problem needs the retry rule of
+    ``factor_hessian``."""
+    _require_cuda(hs, "hessians")
+    if hs.dtype != torch.float32 or hs.dim() != 3 or hs.shape[1] != hs.shape[2] or not hs.is_contiguous():
+        raise TypeError("factor_hessians_batched expects a contiguous fp32 [B, n, n] tensor")
+    batch, n, _ = hs.shape
+    dev = hs.device
+    out = {"u": torch.empty((batch, n, n), dtype=torch.float32, device=dev),
+           "perm": torch.empty((batch, n), dtype=torch.int32, device=dev),
+           "invperm": torch.empty((batch, n), dtype=torch.int32, device=dev),
+           "dead": torch.empty((batch, n), dtype=torch.uint8, device=dev),
+           "damp": torch.empty((batch, 2), dtype=torch.float32, device=dev),
+           "status": torch.empty(batch, dtype=torch.int32, device=dev)}
+    with torch.cuda.device(dev):
+        ws = _workspace(_lib.load().oc_hinv_workspace_bytes(n) * batch, dev)
+        call("oc_hinv_factor_batched", batch, ptr(hs), n, float(percdamp), 1 if actorder else 0, ptr(out["u"]),
+             ptr(out["perm"]), ptr(out["invperm"]), ptr(out["dead"]), ptr(out["damp"]), ptr(out["status"]),
+             ptr(ws), ws.numel(), stream_handle())
+    return out
+
+
 def factor_hessian_launch(h: torch.Tensor, percdamp: float, actorder: bool, buffers: Optional[dict] = None) -> dict:
     """First attempt of ``factor_hessian`` enqueued on the current stream without waiting for its
     status: lets several small factorisations run side by side on different streams.  Finish

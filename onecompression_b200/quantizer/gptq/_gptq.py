@@ -383,9 +383,9 @@ class GPTQ(Quantizer):
     def independent_on_device(self, items):
         """Factor and quantize layers that each come with a Hessian of their own (``items`` =
         [(module, hessian)], no weight correction).  Layers of equal shape and settings are batched:
-        their factors are written into one array and one chain of column-loop launches serves all of
-        them (``kernels.gptq_quantize_batched``), with a single device synchronisation for the
-        statuses of the factorisations.  Returns, in the order of ``items``, dicts with the device
+        one chain of factorisation launches (``kernels.factor_hessians_batched``) and one chain of
+        column-loop launches (``kernels.gptq_quantize_batched``) serve all of them, with a single
+        device synchronisation for the statuses of the factorisations.  Returns, in the order of ``items``, dicts with the device
         outputs (qweight / qzeros or codes / zeros, scales, dequantized) plus ``perm`` (int64 or
         None), ``bits``, ``gs``, ``seconds``; everything is complete on return."""
         if not items:
@@ -410,17 +410,12 @@ class GPTQ(Quantizer):
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
             weights = torch.stack([_weight_matrix(items[i][0]) for i in idxs]).contiguous()
-            u = torch.empty((batch, d, d), dtype=torch.float32, device=dev)
-            perm = torch.empty((batch, d), dtype=torch.int32, device=dev)
-            invperm = torch.empty((batch, d), dtype=torch.int32, device=dev)
-            dead = torch.empty((batch, d), dtype=torch.uint8, device=dev)
-            pending = [kernels.factor_hessian_launch(
-                items[i][1].to(dev), self.percdamp, self.actorder,
-                buffers={"u": u[b], "perm": perm[b], "invperm": invperm[b], "dead": dead[b]})
-                for b, i in enumerate(idxs)]
-            status = torch.cat([p["status"] for p in pending]).cpu()       # the one synchronisation
+            hs = torch.stack([items[i][1].to(device=dev, dtype=torch.float32) for i in idxs]).contiguous()
+            fact = kernels.factor_hessians_batched(hs, self.percdamp, self.actorder)
+            u, perm, invperm, dead = fact["u"], fact["perm"], fact["invperm"], fact["dead"]
+            status = fact["status"].cpu()                                   # the one synchronisation
             for b in torch.nonzero(status).flatten().tolist():
-                fac = kernels.factor_hessian(pending[b]["h"], self.percdamp, self.actorder)   # retry rule
+                fac = kernels.factor_hessian(hs[b], self.percdamp, self.actorder)   # retry rule
                 u[b].copy_(fac.u)
                 perm[b].copy_(fac.perm)
                 invperm[b].copy_(fac.invperm)
