@@ -775,3 +775,48 @@ def test_moe_block_with_batched_experts_matches_serial_path():
         for f in ("qweight", "qzeros", "scales"):
             assert torch.equal(getattr(r, f), getattr(s, f)), (name, f)
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+def test_saved_mixed_precision_model_round_trip(tmp_path):
+    """AutoBit result saved and loaded: per-module bit widths travel in quantization_config and the
+    reloaded model gives the same logits."""
+    import json
+
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep._quantize_with_qep_arch import run_quantize_with_qep_arch
+    from onecompression_b200.quantizer.autobit import AutoBitQuantizer
+    from onecompression_b200.utils import load_quantized_layers, save_quantized_model
+
+    def fresh():
+        torch.manual_seed(5)
+        cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=2,
+                          num_hidden_layers=1, vocab_size=512, max_position_embeddings=128,
+                          tie_word_embeddings=False)
+        m = LlamaForCausalLM(cfg).half().to(DEV).eval()
+        with torch.no_grad():
+            m.model.layers[0].mlp.down_proj.weight.mul_(4.0)
+            m.model.layers[0].self_attn.o_proj.weight.mul_(0.25)
+        return m
+
+    model = fresh()
+    ids = torch.randint(0, 512, (32, 64), device=DEV)
+    auto = AutoBitQuantizer(quantizers=[GPTQ(wbits=b, groupsize=32, sym=False) for b in (2, 3, 4)], target_bit=3.0)
+    run_quantize_with_qep_arch(None, auto, QEPConfig(device=DEV), None, model=model,
+                               model_inputs={"input_ids": ids}, report_progress=False)
+    bits = {n: r.wbits for n, r in auto.results.items()}
+    assert len(set(bits.values())) > 1
+    model.to(DEV)
+    with torch.no_grad():
+        want = model(input_ids=ids[:4]).logits.float().cpu()
+    save_quantized_model(model, auto, str(tmp_path))
+    qcfg = json.load(open(tmp_path / "config.json"))["quantization_config"]
+    assert qcfg["quant_method"] == "mixed_gptq" and qcfg["module_wbits"] == bits
+    assert qcfg["quantization_bits"][0]["mlp.down_proj"]["bits"] == bits["model.layers.0.mlp.down_proj"]
+    again, _ = load_quantized_layers(fresh(), str(tmp_path))
+    for n, b in bits.items():
+        assert dict(again.named_modules())[n].wbits == b
+    with torch.no_grad():
+        got = again(input_ids=ids[:4]).logits.float().cpu()
+    assert torch.equal(want, got)
