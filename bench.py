@@ -410,6 +410,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # torchrun pins every rank to one host thread; rank 0 alone works here and takes the
+        # cores a single process would get (one thread per physical core, as torch's default)
+        n = os.cpu_count() or 1
+        torch.set_num_threads(max(1, min(32, n // 2 if n > 16 else n)))
     tokens, out, d = 4 * SEQ_LEN, 4096, 4096
     for _ in range(min(args.warmup, 1)):
         _cpu_sample(SEQ_LEN, 1024, 1024)
