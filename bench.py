@@ -302,7 +302,8 @@ def run_ours(args):
     k_ms = e0.elapsed_time(e1) / reps
     tiles_h = sum(d // 256 - (tm >> 1) for tm in range(d // 128))
     tiles_c = (d // 128) * (d // 256)
-    executed = (tiles_h + tiles_c) * 128 * 256 * 2.0 * ntok
+    # every tile of C runs two accumulation chains per chunk (Xf - Xq is carried as two 16-bit terms)
+    executed = (tiles_h + 2 * tiles_c) * 128 * 256 * 2.0 * ntok
     algorithmic = 2 * 2.0 * ntok * d * d
     peaks = _peaks()
     achieved = executed / (k_ms * 1e-3) / 1e12
@@ -343,7 +344,7 @@ def run_ours(args):
             "traffic": round(0.20e9 + 0.90e9 * ntok / 16384),
             "traffic_note": "scaled from the ncu capture of a 16384-token launch (profiles/)",
             "peak_source": peaks["src"] + " (burst: kernel timed alone)",
-            "flops": "executed MMA flops (upper tiles of H, all of C)",
+            "flops": "executed MMA flops (upper tiles of H, all of C twice: two 16-bit terms of Xf - Xq)",
             "hessian_gemm_tflops_algorithmic": round(algorithmic / (k_ms * 1e-3) / 1e12, 1),
             "ms_per_launch": round(k_ms, 4),
         },

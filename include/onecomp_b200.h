@@ -57,9 +57,14 @@ long long oc_launch_count_reset(void);
  * and _compute_per_module_hessians (:252-262).  The running mean of the
  * reference is a_old = n/(n+t), a_new = 2/(n+t).
  *
+ * xq and xf are read with the same row stride ld.
+ *
  * Tensor-core path (tcgen05 + TMA): taken when d, ld are multiples of 8, ldh of 4,
  * pointers 16-byte aligned, n_tok > 0, status != NULL and (for C) delta_scratch
- * ([n_tok, ld] fp16) is given.  It writes only the tiles of H that touch the upper
+ * (2 * n_tok * d 16-bit elements) is given: it receives Xf - Xq as two 16-bit terms
+ * (the rounded difference and its rounding error), so that the product uses the fp32
+ * difference the reference forms (:885) to about 2^-22 (fp16) / 2^-16 (bf16) relative, not
+ * its 16-bit rounding.  The path writes only the tiles of H that touch the upper
  * triangle: call oc_mirror_upper(H) once after the last accumulation.  C is
  * written in full.  Any other shape runs an fp32 FMA kernel that writes H in full.
  * chunk_tokens (0 = 512): tokens per tensor-core accumulation chain.
@@ -76,11 +81,12 @@ int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long lo
  * counterpart in the reference, which allocates freely through torch).  A host that runs
  * inside another runtime's stream capture, inside a memory pool it does not own, or under a
  * rule that its device footprint must not grow after start-up cannot provide delta_scratch;
- * here that scratch is a fixed 32 MiB device array inside the library image, held on every
+ * here that scratch is a fixed 64 MiB device array inside the library image, held on every
  * GPU that loads the library until the process exits.  Inputs and outputs are still the
  * caller's.  Limits and rules:
- *   - with C != NULL, n_tok * ld must not exceed oc_moment_static_capacity() (16 Mi fp16
- *     elements); larger calls return OC_ERR_TOO_LARGE: feed the tokens in several calls;
+ *   - with C != NULL, n_tok * ld must not exceed oc_moment_static_capacity() (16 Mi
+ *     activation elements; the array holds two 16-bit terms for each); larger calls return
+ *     OC_ERR_TOO_LARGE: feed the tokens in several calls;
  *   - the first call on each device looks up the array's device address (with that device
  *     current); make that first call outside any stream capture;
  *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating routine;

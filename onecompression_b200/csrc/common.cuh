@@ -57,6 +57,26 @@ __device__ __forceinline__ void oc_st16(void* p, long long i, float v, int bf16)
 
 static inline int oc_div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) and device
+// properties belong to a device, and one process may drive several: keep "done" flags and cached
+// values per device.  OC_MAX_DEVICES bounds the tables; OC_CURRENT_DEVICE(dev) fetches the index.
+#define OC_MAX_DEVICES 64
+#define OC_CURRENT_DEVICE(dev)                                            \
+  int dev = 0;                                                            \
+  OC_CUDA(cudaGetDevice(&dev));                                           \
+  OC_REQUIRE(dev >= 0 && dev < OC_MAX_DEVICES, "device index out of range")
+
+// Raises the dynamic shared memory limit of `kernel` to `bytes` once per device.
+#define OC_OPT_IN_SMEM(kernel, bytes)                                                             \
+  do {                                                                                            \
+    static bool done__[OC_MAX_DEVICES] = {};                                                      \
+    OC_CURRENT_DEVICE(dev__);                                                                     \
+    if (!done__[dev__]) {                                                                         \
+      OC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));  \
+      done__[dev__] = true;                                                                       \
+    }                                                                                             \
+  } while (0)
+
 // ---- engines of oc_moment_accum (its `engine` argument) ---------------------
 enum : int {
   OC_MOMENT_AUTO = 0,    // tensor cores when the shapes allow, else FMA

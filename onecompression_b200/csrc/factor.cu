@@ -339,12 +339,8 @@ static int hinv_factor_impl(int batch, const float* H, long long ldh, int n, flo
     OC_CUDA(cudaMemsetAsync(X + b * sW, 0, (size_t)n * ld * sizeof(float), stream));
 
   // ---- blocked right-looking Cholesky --------------------------------------------------
-  static bool attr_set = false;
   const int smem = (2 * NB * (NB + 1) + (NB / 2) * (NB / 2)) * (int)sizeof(float);
-  if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(potrf_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
-  }
+  OC_OPT_IN_SMEM(potrf_diag_kernel, smem);
   auto batched = [&](OcGemm& g) { g.batch = batch; g.strideA = sW; g.strideB = sW; g.strideC = sW; };
   // Two levels: inside an outer block of OB columns every 128-column panel updates only the
   // rest of that outer block (full height); the matrix behind the outer block is updated once per

@@ -337,18 +337,14 @@ int make_operand_map(CUtensorMap* map, const float* ptr, bool mn_major, int rows
 
 template <bool A_MN, bool B_MN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, int grid, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    attr_set = true;
-  }
+  OC_OPT_IN_SMEM((gemm_tf32x3_kernel<A_MN, B_MN>), SMEM_DYN);
   gemm_tf32x3_kernel<A_MN, B_MN><<<grid, NUM_THREADS, SMEM_DYN, s>>>(ma, mb, p);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }
 
-int g_sm_count = 0;
-int* g_status[64] = {};
+int g_sm_count[OC_MAX_DEVICES] = {};
+int* g_status[OC_MAX_DEVICES] = {};
 
 }  // namespace
 
@@ -366,16 +362,14 @@ bool oc_gemm_tc_eligible(const OcGemm& g) {
 }
 
 int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
-  int dev = 0;
-  OC_CUDA(cudaGetDevice(&dev));
-  OC_REQUIRE(dev >= 0 && dev < 64, "gemm: device index out of range");
+  OC_CURRENT_DEVICE(dev);
   if (!g_status[dev]) {
     void* p = nullptr;
     OC_CUDA(cudaGetSymbolAddress(&p, g_gemm_status_word));
     g_status[dev] = (int*)p;
   }
-  if (g_sm_count == 0) {
-    OC_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  if (g_sm_count[dev] == 0) {
+    OC_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
   }
   CUtensorMap ma, mb;
   int rc = make_operand_map(&ma, g.A, g.transA != 0, g.M, g.K, g.lda, g.strideA, g.batch);
@@ -390,7 +384,7 @@ int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   p.status = g_status[dev];
   const long long items = (long long)p.batch * p.tiles_m * p.tiles_n;
   OC_REQUIRE(items < (1ll << 30), "gemm: too many tiles");
-  const int grid = (int)((items < g_sm_count) ? items : g_sm_count);
+  const int grid = (int)((items < g_sm_count[dev]) ? items : g_sm_count[dev]);
   const bool a_mn = g.transA != 0, b_mn = g.transB == 0;
   if (a_mn) return b_mn ? launch<true, true>(ma, mb, p, grid, stream) : launch<true, false>(ma, mb, p, grid, stream);
   return b_mn ? launch<false, true>(ma, mb, p, grid, stream) : launch<false, false>(ma, mb, p, grid, stream);

@@ -390,12 +390,8 @@ __global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ code
 
 template <int WARPS, bool ALIGNED>
 int launch_block_t(const ColArgs& a, cudaStream_t stream) {
-  static bool attr_set = false;
   const int smem = (BLK * BLK + WARPS * 32 * WS) * (int)sizeof(float);
-  if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(gptq_block_kernel<WARPS, ALIGNED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
-  }
+  OC_OPT_IN_SMEM((gptq_block_kernel<WARPS, ALIGNED>), smem);
   gptq_block_kernel<WARPS, ALIGNED><<<dim3(oc_div_up(a.out, WARPS * 32), a.batch), LOADERS, smem, stream>>>(a);
   OC_CHECK_LAUNCH();
   return OC_OK;

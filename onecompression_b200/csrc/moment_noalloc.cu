@@ -1,19 +1,20 @@
 // Second moments for callers that cannot allocate device memory.
 //
-// oc_moment_accum needs a caller-provided fp16 scratch of n_tok x ld elements whenever the
-// cross term C is requested (it holds Xf - Xq for the tensor-core kernel).  Some hosts cannot
+// oc_moment_accum needs a caller-provided 16-bit scratch of 2 x n_tok x d elements whenever the
+// cross term C is requested (it holds Xf - Xq as two 16-bit terms for the tensor-core kernel).  Some hosts cannot
 // hand one over: a plugin that is called from inside somebody else's CUDA-graph capture or
 // from a context whose memory pool is owned and sized by another runtime, or a process that
 // is forbidden to grow its device footprint after start-up, cannot call cudaMalloc at that
 // point.  For them this file keeps the scratch in a fixed, file-scope device array that is
-// part of the library image: every GPU on which the library is loaded holds these 32 MiB
+// part of the library image: every GPU on which the library is loaded holds these 64 MiB
 // until the process exits, and in exchange the call below allocates nothing at all.
 #include "common.cuh"
 
-// capacity of the built-in scratch, in fp16 elements (32 MiB)
+// capacity of the built-in scratch: activation elements (n_tok x ld) per call; the array holds
+// two 16-bit terms for each (64 MiB)
 #define OC_STATIC_SCRATCH_HALFS (16ll * 1024 * 1024)
 
-static __device__ __align__(256) __half g_static_delta_scratch[OC_STATIC_SCRATCH_HALFS];
+static __device__ __align__(256) __half g_static_delta_scratch[2 * OC_STATIC_SCRATCH_HALFS];
 
 extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok,
                                int d, long long ld, float* H, float* C, long long ldh, float a_old,

@@ -82,24 +82,42 @@ __global__ void __launch_bounds__(256) moment_simt_kernel(const void* __restrict
     }
 }
 
-// delta = round16( float(xf) - float(xq) ) in the activations' own 16-bit type; exact whenever
-// the two values are within a factor of two of each other, which is the rule for a quantisation
-// perturbation.
-__global__ void delta_f16_kernel(const __half2* __restrict__ xf, const __half2* __restrict__ xq,
-                                 __half2* __restrict__ out, long long n2) {
+// D = float(xf) - float(xq) as two planes in the activations' own 16-bit type:
+//   hi = round16(D)                 (exact whenever the two values are within a factor of two)
+//   lo = round16((D - hi) * lo_up)  (the rounding error of hi, scaled up into the normal range)
+// Rows are read ld elements apart and written packed (d elements apart); eight elements per thread.
+template <typename T2>
+__device__ __forceinline__ float2 oc_cvt2(T2 v);
+template <> __device__ __forceinline__ float2 oc_cvt2<__half2>(__half2 v) { return __half22float2(v); }
+template <> __device__ __forceinline__ float2 oc_cvt2<__nv_bfloat162>(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename T2>
+__device__ __forceinline__ T2 oc_rnd2(float a, float b);
+template <> __device__ __forceinline__ __half2 oc_rnd2<__half2>(float a, float b) { return __floats2half2_rn(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 oc_rnd2<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+
+template <typename T2>
+__global__ void delta_split_kernel(const uint4* __restrict__ xf, const uint4* __restrict__ xq, long long ld8,
+                                   uint4* __restrict__ hi, uint4* __restrict__ lo, long long n_tok, int d8,
+                                   float lo_up) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n2) return;
-  const float2 f = __half22float2(xf[i]);
-  const float2 q = __half22float2(xq[i]);
-  out[i] = __floats2half2_rn(f.x - q.x, f.y - q.y);
-}
-__global__ void delta_bf16_kernel(const __nv_bfloat162* __restrict__ xf, const __nv_bfloat162* __restrict__ xq,
-                                  __nv_bfloat162* __restrict__ out, long long n2) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n2) return;
-  const float2 f = __bfloat1622float2(xf[i]);
-  const float2 q = __bfloat1622float2(xq[i]);
-  out[i] = __floats2bfloat162_rn(f.x - q.x, f.y - q.y);
+  if (i >= n_tok * d8) return;
+  const long long t = i / d8;
+  const int c = (int)(i - t * d8);
+  union V { uint4 u; T2 h[4]; };
+  V f, q, oh, ol;
+  f.u = xf[t * ld8 + c];
+  q.u = xq[t * ld8 + c];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 a = oc_cvt2<T2>(f.h[k]), b = oc_cvt2<T2>(q.h[k]);
+    const float dx = a.x - b.x, dy = a.y - b.y;
+    const T2 h = oc_rnd2<T2>(dx, dy);
+    const float2 hf = oc_cvt2<T2>(h);
+    oh.h[k] = h;
+    ol.h[k] = oc_rnd2<T2>((dx - hf.x) * lo_up, (dy - hf.y) * lo_up);
+  }
+  hi[i] = oh.u;
+  lo[i] = ol.u;
 }
 
 // lower <- upper (mirror across the diagonal), 32x32 tiles
@@ -145,16 +163,23 @@ int oc_moment_simt_launch(const void* xq, const void* xf, int bf16, long long n_
   return OC_OK;
 }
 
-int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, int bf16, cudaStream_t stream) {
-  OC_REQUIRE(xf && xq && out && n >= 0 && n % 2 == 0, "delta_f16: null pointer or odd length");
-  if (n == 0) return OC_OK;
-  const long long n2 = n / 2;
+// out = [2][n_tok][d]: the hi plane, then the lo plane.  d and ld multiples of 8, all pointers
+// 16-byte aligned (the conditions of the tensor-core path).
+int oc_delta_split_launch(const void* xf, const void* xq, long long ld, void* out, long long n_tok, int d,
+                          int bf16, float lo_up, cudaStream_t stream) {
+  OC_REQUIRE(xf && xq && out && n_tok >= 0 && d % 8 == 0 && ld % 8 == 0, "delta_split: bad arguments");
+  if (n_tok == 0) return OC_OK;
+  const int d8 = d / 8;
+  const long long n = n_tok * d8;
+  uint4* hi = (uint4*)out;
+  uint4* lo = hi + n;
+  const unsigned grid = (unsigned)((n + 255) / 256);
   if (bf16)
-    delta_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, stream>>>(
-        (const __nv_bfloat162*)xf, (const __nv_bfloat162*)xq, (__nv_bfloat162*)out, n2);
+    delta_split_kernel<__nv_bfloat162><<<grid, 256, 0, stream>>>((const uint4*)xf, (const uint4*)xq, ld / 8, hi, lo,
+                                                               n_tok, d8, lo_up);
   else
-    delta_f16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, stream>>>(
-        (const __half2*)xf, (const __half2*)xq, (__half2*)out, n2);
+    delta_split_kernel<__half2><<<grid, 256, 0, stream>>>((const uint4*)xf, (const uint4*)xq, ld / 8, hi, lo, n_tok,
+                                                        d8, lo_up);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }

@@ -1,7 +1,7 @@
 // Tensor-core second moments on sm_100a: tcgen05.mma with TMEM accumulators, fed by TMA.
 //
 //   H <- a_old * H + a_new * Xq^T Xq          (upper tiles only; mirror afterwards)
-//   C <- a_old * C + a_new * D^T  Xq          (D = fp16(Xf - Xq), full square)
+//   C <- a_old * C + a_new * D^T  Xq          (D = Xf - Xq carried as two 16-bit terms, full square)
 //
 // Reference call sites: onecomp/quantizer/_quantizer.py:824-830 (Hessian),
 // onecomp/qep/_quantize_with_qep_arch.py:182-196 (Hessian + cross term).
@@ -25,6 +25,17 @@
 //                 accumulates: measured relative bias of a sum of squares is
 //                 about -4.7e-9 per token of chain length, so 512 tokens keep
 //                 H within 2.2e-6 of the exact moment.)
+// The difference D = float(Xf) - float(Xq) is what the reference multiplies (in fp32).  One
+// 16-bit value holds it exactly only while the two activations are within a factor of two of
+// each other; after a few quantized blocks many are not.  D is therefore carried as
+// hi = round16(D) and lo = round16((D - hi) * 2^k) (k = 11 for fp16, 8 for bf16: lo is scaled into
+// the normal range).  For the tiles of C every chunk of tokens is accumulated twice, once with hi
+// and once with lo as the left operand, each in a TMEM chain of its own, and the drain warps add
+// the lo chain times 2^-k.
+//
+// Work items are ordered so that CTAs running at the same time share operand panels (super-columns
+// of eight 256-column panels, swept row by row), first the tiles of C (two chains per chunk), then
+// the upper tiles of H.
 // Every mbarrier wait is bounded: after about two seconds the CTA raises an
 // abort flag, records a code in *status and tears down normally.
 #include "tc_common.cuh"
@@ -46,7 +57,9 @@ struct MomentParams {
   int d; long long n_tok;
   float a_old, a_new;
   int chunk_stages;   // stages (of BK tokens) per TMEM accumulation chunk
-  int h_tiles, c_tiles, tiles_n;
+  int h_tiles, c_tiles, tiles_m, tiles_n;
+  int c_planes;       // 16-bit terms of D (2: hi and scaled lo)
+  float lo_scale;     // factor that undoes the scaling of the lo term
   uint32_t idesc;     // IDESC, plus the bf16 operand-format bits for bf16 activations
   int* status;
 };
@@ -68,20 +81,34 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
       "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-// work item -> (matrix, first row, first column)
+// work item -> (matrix, first row, first column).  Items 0 .. c_tiles-1 are the tiles of C, the
+// rest the tiles of H that touch the upper triangle (row tile tm owns column tiles >= tm/2).
+// Both are enumerated super-column by super-column (SCW column tiles wide), row by row inside.
+constexpr int SCW = 8;
 __device__ __forceinline__ void decode_item(const MomentParams& p, int item, int& is_c, int& m0, int& n0) {
-  if (item < p.h_tiles) {
-    // upper enumeration: row tile tm owns column tiles tm/2 .. tiles_n-1
-    int tm = 0, left = item;
-    for (;; ++tm) {
-      const int cnt = p.tiles_n - (tm >> 1);
-      if (left < cnt) break;
+  if (item < p.c_tiles) {
+    const int full = p.tiles_n / SCW, per_sc = p.tiles_m * SCW;
+    int tm, tn;
+    if (item < full * per_sc) {
+      const int sc = item / per_sc, r = item - sc * per_sc;
+      tm = r / SCW; tn = sc * SCW + r % SCW;
+    } else {
+      const int k = item - full * per_sc, w = p.tiles_n - full * SCW;
+      tm = k / w; tn = full * SCW + k % w;
+    }
+    is_c = 1; m0 = tm * TILE_M; n0 = tn * TILE_N;
+    return;
+  }
+  int left = item - p.c_tiles;
+  is_c = 0; m0 = 0; n0 = 0;
+  for (int c_lo = 0; c_lo < p.tiles_n; c_lo += SCW) {
+    const int c_hi = min(p.tiles_n, c_lo + SCW);
+    const int rows = min(p.tiles_m, 2 * c_hi);          // row tiles that reach this super-column
+    for (int tm = 0; tm < rows; ++tm) {
+      const int first = max(c_lo, tm >> 1), cnt = c_hi - first;
+      if (left < cnt) { m0 = tm * TILE_M; n0 = (first + left) * TILE_N; return; }
       left -= cnt;
     }
-    is_c = 0; m0 = tm * TILE_M; n0 = ((tm >> 1) + left) * TILE_N;
-  } else {
-    const int k = item - p.h_tiles;
-    is_c = 1; m0 = (k / p.tiles_n) * TILE_M; n0 = (k % p.tiles_n) * TILE_N;
   }
 }
 
@@ -125,18 +152,25 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
         int is_c, m0, n0;
         decode_item(p, item, is_c, m0, n0);
         const CUtensorMap* map_a = is_c ? &map_delta : &map_xq;
-        for (int ks = 0; ks < total_stages; ++ks) {
-          ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 101);
-          if (!ok) break;
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          const uint32_t sa = stage_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_ATOMS * ATOM_BYTES;
-          mbar_expect_tx(full, STAGE_BYTES);
+        const int planes = is_c ? p.c_planes : 1;
+        for (int ch = 0; ch < n_chunks && ok; ++ch) {
+          const int s_begin = ch * p.chunk_stages;
+          const int s_end = min(total_stages, s_begin + p.chunk_stages);
+          for (int pl = 0; pl < planes && ok; ++pl) {
+            for (int ks = s_begin; ks < s_end; ++ks) {
+              ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 101);
+              if (!ok) break;
+              const uint32_t full = smem_u32(&bar_full[stage]);
+              const uint32_t sa = stage_base + stage * STAGE_BYTES;
+              const uint32_t sb = sa + A_ATOMS * ATOM_BYTES;
+              mbar_expect_tx(full, STAGE_BYTES);
 #pragma unroll
-          for (int a = 0; a < A_ATOMS; ++a) tma_load_2d(sa + a * ATOM_BYTES, map_a, m0 + a * 64, ks * BK, full);
+              for (int a = 0; a < A_ATOMS; ++a) tma_load_3d(sa + a * ATOM_BYTES, map_a, m0 + a * 64, ks * BK, pl, full);
 #pragma unroll
-          for (int b = 0; b < B_ATOMS; ++b) tma_load_2d(sb + b * ATOM_BYTES, &map_xq, n0 + b * 64, ks * BK, full);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              for (int b = 0; b < B_ATOMS; ++b) tma_load_3d(sb + b * ATOM_BYTES, &map_xq, n0 + b * 64, ks * BK, 0, full);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
       if (!ok) {
@@ -151,7 +185,10 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
       uint32_t stage = 0, phase = 0, cc = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        for (int ch = 0; ch < n_chunks && ok; ++ch, ++cc) {
+        const int chains = n_chunks * ((item < p.c_tiles) ? p.c_planes : 1);
+        const int planes = (item < p.c_tiles) ? p.c_planes : 1;
+        for (int chain = 0; chain < chains && ok; ++chain, ++cc) {
+          const int ch = chain / planes;
           const uint32_t buf = cc & 1u;
           ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((cc >> 1) & 1u) ^ 1u, abort_flag, p.status, 102);
           if (!ok) break;
@@ -192,18 +229,22 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
       float acc[128];
 #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-      for (int ch = 0; ch < n_chunks; ++ch, ++cc) {
+      const int planes = is_c ? p.c_planes : 1;
+      const int chains = n_chunks * planes;
+      for (int chain = 0; chain < chains; ++chain, ++cc) {
         const uint32_t buf = cc & 1u;
         ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (cc >> 1) & 1u, abort_flag, p.status, 104);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + half * 128;
+        // chains alternate hi, lo; fmaf(v, 1, acc) rounds exactly like v + acc
+        const float scale = (chain % planes) ? p.lo_scale : 1.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float v[64];
           tmem_ld64(taddr + c * 64, v);
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[c * 64 + i] += v[i];
+          for (int i = 0; i < 64; ++i) acc[c * 64 + i] = fmaf(v[i], scale, acc[c * 64 + i]);
         }
         tc_fence_before();
         __syncwarp();
@@ -241,14 +282,15 @@ moment_tc_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_consta
   }
 }
 
-int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long ld, int bf16) {
+// [planes][n_tok][d] 16-bit elements, rows ld elements apart, planes n_tok * ld elements apart
+int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long ld, int planes, int bf16) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { oc_set_last_error("moment: cuTensorMapEncodeTiled is not available"); return OC_ERR_CUDA; }
-  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)n_tok};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)BK};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)n_tok, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)n_tok * (cuuint64_t)ld * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(x), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { oc_set_last_error("moment: cuTensorMapEncodeTiled failed"); return OC_ERR_CUDA; }
@@ -260,11 +302,13 @@ int make_map(CUtensorMap* map, const void* x, long long n_tok, int d, long long 
 int oc_moment_simt_launch(const void* xq, const void* xf, int bf16, long long n_tok, int d, long long ld,
                           float* H, float* C, long long ldh, float a_old, float a_new, cudaStream_t stream);
 
-int oc_delta_f16_launch(const void* xf, const void* xq, void* out, long long n, int bf16, cudaStream_t stream);
+int oc_delta_split_launch(const void* xf, const void* xq, long long ld, void* out, long long n_tok, int d,
+                          int bf16, float lo_scale, cudaStream_t stream);
 
 int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delta, float* H, float* C,
                           long long ldh, int d, long long n_tok, float a_old, float a_new, int chunk_tokens,
-                          int sm_count, int bf16, int* status, cudaStream_t stream);
+                          int sm_count, int bf16, int c_planes, float lo_scale, int* status,
+                          cudaStream_t stream);
 
 // See include/onecomp_b200.h for the contract.
 extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scratch, long long n_tok,
@@ -277,47 +321,48 @@ extern "C" int oc_moment_accum(const void* xq, const void* xf, void* delta_scrat
   OC_REQUIRE(xq && (H || C) && d > 0 && n_tok >= 0 && ld >= d && ldh >= d, "moment_accum: bad arguments");
   OC_REQUIRE(!C || xf, "moment_accum: the cross term needs the full-precision activations");
   const bool tc_ok = engine != OC_MOMENT_SIMT && d % 8 == 0 && ld % 8 == 0 && ldh % 4 == 0 && n_tok > 0 && status &&
-                     ((uintptr_t)xq & 15) == 0 && (!C || (delta_scratch && ((uintptr_t)delta_scratch & 15) == 0)) &&
+                     ((uintptr_t)xq & 15) == 0 &&
+                     (!C || (delta_scratch && ((uintptr_t)delta_scratch & 15) == 0 && ((uintptr_t)xf & 15) == 0)) &&
                      (!H || ((uintptr_t)H & 15) == 0) && (!C || ((uintptr_t)C & 15) == 0);
   if (!tc_ok) {
     // general shapes: fp32 FMA kernel (forms Xf - Xq itself, in fp32)
     return oc_moment_simt_launch(xq, C ? xf : nullptr, bf16, n_tok, d, ld,
                                  H, C, ldh, a_old, a_new, stream);
   }
-  const void* delta_or_xf = nullptr;
+  // D = Xf - Xq as two 16-bit planes [2][n_tok][d] (rows packed to d elements): hi, then lo * 2^k
+  const int c_planes = 2;
+  const float lo_up = bf16 ? 256.f : 2048.f;
   if (C) {
-    int rcd = oc_delta_f16_launch(xf, xq, delta_scratch, n_tok * ld, bf16, stream);
+    int rcd = oc_delta_split_launch(xf, xq, ld, delta_scratch, n_tok, d, bf16, lo_up, stream);
     if (rcd) return rcd;
-    delta_or_xf = delta_scratch;
   }
   CUtensorMap map_xq, map_delta;
-  int rc = make_map(&map_xq, xq, n_tok, d, ld, bf16);
+  int rc = make_map(&map_xq, xq, n_tok, d, ld, 1, bf16);
   if (rc) return rc;
-  if (C) { rc = make_map(&map_delta, delta_or_xf, n_tok, d, ld, bf16); if (rc) return rc; }
+  if (C) { rc = make_map(&map_delta, delta_scratch, n_tok, d, d, c_planes, bf16); if (rc) return rc; }
   else map_delta = map_xq;
 
   if (engine == OC_MOMENT_PAIR || (engine == OC_MOMENT_AUTO && OC_MOMENT_AUTO_USES_PAIRS))
     return oc_moment_pair_launch(map_xq, map_delta, H, C, ldh, d, n_tok, a_old, a_new, chunk_tokens, sm_count,
-                                 bf16, status, stream);
+                                 bf16, c_planes, 1.f / lo_up, status, stream);
 
   MomentParams p{};
   p.H = H; p.C = C; p.ldh = ldh; p.d = d; p.n_tok = n_tok; p.a_old = a_old; p.a_new = a_new;
   if (chunk_tokens <= 0) chunk_tokens = 512;
   p.chunk_stages = max(1, chunk_tokens / BK);
   const int tiles_m = oc_div_up(d, TILE_M);
+  p.tiles_m = tiles_m;
   p.tiles_n = oc_div_up(d, TILE_N);
   int h_tiles = 0;
   if (H) for (int tm = 0; tm < tiles_m; ++tm) h_tiles += max(0, p.tiles_n - (tm >> 1));
   p.h_tiles = h_tiles;
   p.c_tiles = C ? tiles_m * p.tiles_n : 0;
+  p.c_planes = c_planes;
+  p.lo_scale = 1.f / lo_up;
   p.idesc = IDESC | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
   p.status = status;
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(moment_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    attr_set = true;
-  }
+  OC_OPT_IN_SMEM(moment_tc_kernel, SMEM_DYN);
   if (sm_count <= 0) sm_count = 148;
   const int grid = min(sm_count, p.h_tiles + p.c_tiles);
   moment_tc_kernel<<<grid, NUM_THREADS, SMEM_DYN, stream>>>(map_xq, map_delta, p);

@@ -39,6 +39,8 @@ struct PairParams {
   float a_old, a_new;
   int chunk_stages;
   int h_tiles, c_tiles, tiles;   // tiles = tiles per matrix side
+  int c_planes;                  // 16-bit terms of Xf - Xq (see moment_tc.cu)
+  float lo_scale;
   uint32_t idesc;
   int* status;
 };
@@ -64,10 +66,11 @@ __device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
       ::"r"(bar), "h"((unsigned short)3) : "memory");
 }
-__device__ __forceinline__ void tma_pair_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+__device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                                 uint32_t leader_bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar) : "memory");
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(leader_bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_on_leader(uint32_t bar) {
   asm volatile(
@@ -83,19 +86,34 @@ __device__ __forceinline__ uint32_t cluster_rank() {
   return r;
 }
 
-// work item -> (matrix, first row, first column) of a 256 x 256 tile
+// work item -> (matrix, first row, first column) of a 256 x 256 tile: first the tiles of C, then
+// the tiles of H on or above the diagonal (row tile tm owns column tiles >= tm), both enumerated
+// super-column by super-column (SCW column tiles wide), row by row inside, so that pairs running
+// at the same time share operand panels.
+constexpr int SCW = 8;
 __device__ __forceinline__ void decode_item(const PairParams& p, int item, int& is_c, int& m0, int& n0) {
-  if (item < p.h_tiles) {
-    int tm = 0, left = item;          // row tile tm owns column tiles tm .. tiles-1
-    for (;; ++tm) {
-      const int cnt = p.tiles - tm;
-      if (left < cnt) break;
+  if (item < p.c_tiles) {
+    const int full = p.tiles / SCW, per_sc = p.tiles * SCW;
+    int tm, tn;
+    if (item < full * per_sc) {
+      const int sc = item / per_sc, r = item - sc * per_sc;
+      tm = r / SCW; tn = sc * SCW + r % SCW;
+    } else {
+      const int k = item - full * per_sc, w = p.tiles - full * SCW;
+      tm = k / w; tn = full * SCW + k % w;
+    }
+    is_c = 1; m0 = tm * PAIR_M; n0 = tn * PAIR_N;
+    return;
+  }
+  int left = item - p.c_tiles;
+  is_c = 0; m0 = 0; n0 = 0;
+  for (int c_lo = 0; c_lo < p.tiles; c_lo += SCW) {
+    const int c_hi = min(p.tiles, c_lo + SCW);
+    for (int tm = 0; tm < c_hi; ++tm) {
+      const int first = max(c_lo, tm), cnt = c_hi - first;
+      if (left < cnt) { m0 = tm * PAIR_M; n0 = (first + left) * PAIR_N; return; }
       left -= cnt;
     }
-    is_c = 0; m0 = tm * PAIR_M; n0 = (tm + left) * PAIR_N;
-  } else {
-    const int k = item - p.h_tiles;
-    is_c = 1; m0 = (k / p.tiles) * PAIR_M; n0 = (k % p.tiles) * PAIR_N;
   }
 }
 
@@ -144,19 +162,28 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
         decode_item(p, item, is_c, m0, n0);
         const CUtensorMap* map_a = is_c ? &map_delta : &map_xq;
         const int am = m0 + (int)rank * HALF, bn = n0 + (int)rank * HALF;
-        for (int ks = 0; ks < total_stages; ++ks) {
-          ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 201);
-          if (!ok) break;
-          const uint32_t full_local = smem_u32(&bar_full[stage]);
-          const uint32_t sa = stage_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + HALF_ATOMS * ATOM_BYTES;
-          if (leader) mbar_expect_tx(full_local, 2 * STAGE_BYTES);   // both CTAs' copies
-          const uint32_t full_leader = full_local & PEER_MASK;
+        const int planes = is_c ? p.c_planes : 1;
+        for (int ch = 0; ch < n_chunks && ok; ++ch) {
+          const int s_begin = ch * p.chunk_stages;
+          const int s_end = min(total_stages, s_begin + p.chunk_stages);
+          for (int pl = 0; pl < planes && ok; ++pl) {
+            for (int ks = s_begin; ks < s_end; ++ks) {
+              ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 201);
+              if (!ok) break;
+              const uint32_t full_local = smem_u32(&bar_full[stage]);
+              const uint32_t sa = stage_base + stage * STAGE_BYTES;
+              const uint32_t sb = sa + HALF_ATOMS * ATOM_BYTES;
+              if (leader) mbar_expect_tx(full_local, 2 * STAGE_BYTES);   // both CTAs' copies
+              const uint32_t full_leader = full_local & PEER_MASK;
 #pragma unroll
-          for (int a = 0; a < HALF_ATOMS; ++a) tma_pair_load_2d(sa + a * ATOM_BYTES, map_a, am + a * 64, ks * BK, full_leader);
+              for (int a = 0; a < HALF_ATOMS; ++a)
+                tma_pair_load_3d(sa + a * ATOM_BYTES, map_a, am + a * 64, ks * BK, pl, full_leader);
 #pragma unroll
-          for (int b = 0; b < HALF_ATOMS; ++b) tma_pair_load_2d(sb + b * ATOM_BYTES, &map_xq, bn + b * 64, ks * BK, full_leader);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              for (int b = 0; b < HALF_ATOMS; ++b)
+                tma_pair_load_3d(sb + b * ATOM_BYTES, &map_xq, bn + b * 64, ks * BK, 0, full_leader);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
       if (!ok) {
@@ -170,7 +197,10 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
       uint32_t stage = 0, phase = 0, cc = 0;
       bool ok = true;
       for (int item = pair; item < total_items && ok; item += n_pairs) {
-        for (int ch = 0; ch < n_chunks && ok; ++ch, ++cc) {
+        const int planes = (item < p.c_tiles) ? p.c_planes : 1;
+        const int chains = n_chunks * planes;
+        for (int chain = 0; chain < chains && ok; ++chain, ++cc) {
+          const int ch = chain / planes;
           const uint32_t buf = cc & 1u;
           ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((cc >> 1) & 1u) ^ 1u, abort_flag, p.status, 202);
           if (!ok) break;
@@ -208,18 +238,21 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
       float acc[128];
 #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-      for (int ch = 0; ch < n_chunks; ++ch, ++cc) {
+      const int planes = is_c ? p.c_planes : 1;
+      const int chains = n_chunks * planes;
+      for (int chain = 0; chain < chains; ++chain, ++cc) {
         const uint32_t buf = cc & 1u;
         ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (cc >> 1) & 1u, abort_flag, p.status, 204);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * PAIR_N + half * 128;
+        const float scale = (chain % planes) ? p.lo_scale : 1.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float v[64];
           tmem_ld64(taddr + c * 64, v);
 #pragma unroll
-          for (int i = 0; i < 64; ++i) acc[c * 64 + i] += v[i];
+          for (int i = 0; i < 64; ++i) acc[c * 64 + i] = fmaf(v[i], scale, acc[c * 64 + i]);
         }
         tc_fence_before();
         __syncwarp();
@@ -264,7 +297,8 @@ moment_pair_kernel(const __grid_constant__ CUtensorMap map_xq, const __grid_cons
 // when pairs cannot be scheduled on this device, so that the caller can fall back.
 int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delta, float* H, float* C,
                           long long ldh, int d, long long n_tok, float a_old, float a_new, int chunk_tokens,
-                          int sm_count, int bf16, int* status, cudaStream_t stream) {
+                          int sm_count, int bf16, int c_planes, float lo_scale, int* status,
+                          cudaStream_t stream) {
   PairParams p{};
   p.H = H; p.C = C; p.ldh = ldh; p.d = d; p.n_tok = n_tok; p.a_old = a_old; p.a_new = a_new;
   if (chunk_tokens <= 0) chunk_tokens = 512;
@@ -272,13 +306,11 @@ int oc_moment_pair_launch(const CUtensorMap& map_xq, const CUtensorMap& map_delt
   p.tiles = oc_div_up(d, PAIR_M);
   p.h_tiles = H ? p.tiles * (p.tiles + 1) / 2 : 0;
   p.c_tiles = C ? p.tiles * p.tiles : 0;
+  p.c_planes = c_planes;
+  p.lo_scale = lo_scale;
   p.idesc = IDESC | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
   p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    OC_CUDA(cudaFuncSetAttribute(moment_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    attr_set = true;
-  }
+  OC_OPT_IN_SMEM(moment_pair_kernel, SMEM_DYN);
   if (sm_count <= 0) sm_count = 148;
   const int pairs = min(sm_count / 2, p.h_tiles + p.c_tiles);
   if (pairs < 1) return OC_OK;

@@ -95,14 +95,19 @@ class MomentAccumulator:
                 raise ValueError("xf and xq differ in shape")
             if xf.dtype != xq.dtype:
                 xf = xf.to(xq.dtype)
+            if xf.stride(0) != xq.stride(0):
+                # the kernels read both with one row stride
+                xq, xf = xq.contiguous(), xf.contiguous()
         n = self.nsamples
         a_old = n / (n + t)
         a_new = 2.0 / (n + t)
         self.nsamples = n + t
         scratch = None
         if cross and not self.force_simt:
-            if self._scratch is None or self._scratch.numel() < xq.numel():
-                self._scratch = torch.empty(xq.numel(), dtype=xq.dtype, device=self.device)
+            # Xf - Xq as two 16-bit terms, rows packed: [2, t, d]
+            need = 2 * t * self.d
+            if self._scratch is None or self._scratch.numel() < need or self._scratch.dtype != xq.dtype:
+                self._scratch = torch.empty(need, dtype=xq.dtype, device=self.device)
             scratch = self._scratch
         with torch.cuda.device(self.device):
             call(
@@ -222,6 +227,7 @@ def factor_hessian(h: torch.Tensor, percdamp: float, actorder: bool, max_retries
                 ptr(dead), ptr(damp), ptr(status), ptr(ws), ws.numel(), stream_handle(),
             )
             if int(status.item()) == 0:
+                check_gemm_status()
                 return HessianFactor(u, perm, invperm, dead, damp, bool(actorder), float(percdamp),
                                      rel, attempt + 1)
             mult *= 10.0
@@ -677,6 +683,8 @@ class _HostCopier:
         outs = list(tensors)
         if not todo:
             return outs
+        if any(t.device != todo[0][1].device for _i, t in todo):
+            raise ValueError("to_host: the tensors of one call must live on one device")
         if self._thread is None or not self._thread.is_alive():
             self._thread = self._threading.Thread(target=self._worker, daemon=True)
             self._thread.start()
@@ -691,16 +699,18 @@ class _HostCopier:
             buf = torch.empty(max(total, 64 << 20), dtype=torch.uint8, pin_memory=True)
             self._bufs[slot] = buf
         pairs, off = [], 0
-        for (i, t), sz in zip(todo, sizes):
-            nbytes = t.numel() * t.element_size()
-            view = buf[off : off + nbytes].view(t.dtype).view(t.shape)
-            view.copy_(t.contiguous(), non_blocking=True)
-            dst = torch.empty(t.shape, dtype=t.dtype)
-            pairs.append((dst, view))
-            outs[i] = dst
-            off += sz
-        event = torch.cuda.Event()
-        event.record()
+        # the copies and the event that guards them go to the tensors' own device
+        with torch.cuda.device(todo[0][1].device):
+            for (i, t), sz in zip(todo, sizes):
+                nbytes = t.numel() * t.element_size()
+                view = buf[off : off + nbytes].view(t.dtype).view(t.shape)
+                view.copy_(t.contiguous(), non_blocking=True)
+                dst = torch.empty(t.shape, dtype=t.dtype)
+                pairs.append((dst, view))
+                outs[i] = dst
+                off += sz
+            event = torch.cuda.Event()
+            event.record()
         done = self._threading.Event()
         self._busy[slot] = done
         self._pending.append(done)
@@ -755,6 +765,15 @@ def set_gemm_engine(mode: int) -> int:
 
 def gemm_tc_status() -> int:
     return _lib.load().oc_gemm_tc_status()
+
+
+def check_gemm_status():
+    """Raise if a tensor-core product on the current device gave up on a bounded pipeline wait
+    (its result, and everything computed from it, is invalid).  Reads one device word, so call it
+    where the host has synchronised anyway."""
+    code = gemm_tc_status()
+    if code != 0:
+        raise RuntimeError(f"fp32 tensor-core product: a bounded pipeline wait expired (code {code})")
 
 
 def gemm_f32(a, b, c=None, alpha=1.0, beta=0.0, trans_a=False, trans_b=False, flags=0):

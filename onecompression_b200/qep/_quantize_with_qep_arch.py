@@ -892,4 +892,9 @@ def run_quantize_with_qep_arch(model_config, quantizer: Quantizer, qep_config: Q
         mse = F.mse_loss(inps_q.float(), inps_f.float()).item()
         logger.info("Block %d MSE: %.6e", idx + 1, mse)
         block_q.cpu()
+    # every factorisation checks the status word of the fp32 tensor-core products issued before it;
+    # this covers the products of the last layers
+    with torch.cuda.device(device):
+        torch.cuda.synchronize(device)
+        kernels.check_gemm_status()
     quantizer.execute_post_processing()

@@ -70,6 +70,19 @@ def _qep_shift_rule(percdamp_mean_ratio=None):
     return rule
 
 
+def qep_factor(hessian, factor, percdamp):
+    """The inverse-Hessian factor the QEP correction may use.  The correction damps with its own
+    ``percdamp`` and has its own retry rule (reference adjust_weight, _quantizer.py:396-428), so a
+    factor made for the column loop serves only if it was built with the same damping and
+    succeeded at the first attempt; otherwise the Hessian is factored again under the correction's
+    rule."""
+    usable = (factor is not None and factor.attempts == 1
+              and abs(factor.percdamp - percdamp) < 1e-12)
+    if usable:
+        return factor
+    return kernels.factor_hessian(hessian, percdamp, actorder=False, shifts=_qep_shift_rule())
+
+
 @dataclass
 class Quantizer(metaclass=ABCMeta):
     """Abstract quantizer (fields and defaults as _quantizer.py:171-201).
@@ -187,11 +200,7 @@ class Quantizer(metaclass=ABCMeta):
             raise RuntimeError("adjust_weight: the module must live on a CUDA device (no CPU path)")
         hessian = hessian.to(weight.device)
         delta_hatx = delta_hatx.to(weight.device)
-        usable = (
-            factor is not None and factor.attempts == 1 and abs(factor.percdamp - percdamp) < 1e-12
-        )
-        if not usable:
-            factor = kernels.factor_hessian(hessian, percdamp, actorder=False, shifts=_qep_shift_rule())
+        factor = qep_factor(hessian, factor, percdamp)
         w16 = weight if weight.dtype in (torch.float16, torch.bfloat16) else weight.to(torch.float16)
         w16 = w16.contiguous() if w16.stride(-1) != 1 else w16
         kernels.qep_adjust(w16, delta_hatx, factor, perccorr)

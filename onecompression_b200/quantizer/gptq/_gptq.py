@@ -331,11 +331,9 @@ class GPTQ(Quantizer):
         stacked = torch.cat([m.weight.data for m in modules], dim=0)
         rows = [m.weight.shape[0] for m in modules]
         if delta_hatX is not None:
-            from .._quantizer import _qep_shift_rule
+            from .._quantizer import qep_factor
 
-            fac = factor
-            if not (fac.attempts == 1 and abs(fac.percdamp - percdamp) < 1e-12 and not fac.actorder):
-                fac = kernels.factor_hessian(hessian, percdamp, actorder=False, shifts=_qep_shift_rule())
+            fac = qep_factor(hessian, factor, percdamp)
             kernels.qep_adjust(stacked, delta_hatX.to(stacked.device), fac, perccorr)
             r0 = 0
             for m, r in zip(modules, rows):        # the corrected weight is the module's weight now

@@ -113,23 +113,34 @@ class ShardedContext:
         slab = weight[first:last]
 
         default_compute = compute is None
+        # results are packed exactly when the quantizer packs on one GPU
+        want_packed = bool(getattr(quantizer, "bitpack_on_quantize", True))
         if compute is None:
+            from .quantizer._quantizer import qep_factor
+
             def compute(w_slab, cross, w_hat_out=None):
                 if w_slab.shape[0] == 0:
                     groups = 1 if gs == -1 else (d + gs - 1) // gs
                     dev = w_slab.device
-                    return {
-                        "qweight": torch.empty((d * bits // 32, 0), dtype=torch.int32, device=dev),
-                        "qzeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
+                    empty = {
                         "scales": torch.empty((groups, 0), dtype=torch.float16, device=dev),
                         "zeros": torch.empty((groups, 0), dtype=torch.int32, device=dev),
                         "dequantized": torch.empty((0, d), dtype=w_slab.dtype, device=dev),
                     }
+                    if want_packed:
+                        empty["qweight"] = torch.empty((d * bits // 32, 0), dtype=torch.int32, device=dev)
+                        empty["qzeros"] = torch.empty((groups, 0), dtype=torch.int32, device=dev)
+                    else:
+                        empty["codes"] = torch.empty((0, d), dtype=torch.int32, device=dev)
+                    return empty
                 if cross is not None:
-                    kernels.qep_adjust(w_slab, cross, factor, cfg.perccorr)
+                    # the correction has its own damping and retry rule: reuse the column loop's
+                    # factor only where one GPU would (same bytes on every rank either way)
+                    kernels.qep_adjust(w_slab, cross, qep_factor(h, factor, cfg.percdamp), cfg.perccorr)
                 outputs = {"dequantized": w_hat_out} if w_hat_out is not None else None
                 return kernels.gptq_quantize(w_slab, factor, wbits=bits, groupsize=gs, sym=quantizer.sym,
-                                             blocksize=quantizer.blocksize, pack=True, outputs=outputs,
+                                             blocksize=quantizer.blocksize, pack=want_packed,
+                                             want_codes=not want_packed, outputs=outputs,
                                              mse=bool(quantizer.mse), q_grid=quantizer.q_grid,
                                              q_norm=quantizer.q_norm)
 
@@ -145,13 +156,24 @@ class ShardedContext:
         else:
             local = compute(slab, c)
             w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
-        qweight = self.gather_rows(local["qweight"], out_features, dim=1)
-        qzeros = self.gather_rows(local["qzeros"], out_features, dim=1, per_row=bits / 32.0)
+        packed = "qweight" in local
+        if packed:
+            qweight = self.gather_rows(local["qweight"], out_features, dim=1)
+            qzeros = self.gather_rows(local["qzeros"], out_features, dim=1, per_row=bits / 32.0)
+        else:
+            # bit widths without a packed layout (or bitpack_on_quantize=False): integer codes
+            # [rows, in] and raw zero points [G, rows], as on one GPU
+            qweight = self.gather_rows(local["codes"], out_features, dim=0)
+            qzeros = self.gather_rows(local["zeros"], out_features, dim=1)
         scales = self.gather_rows(local["scales"], out_features, dim=1)
         perm = getattr(factor, "perm", None) if quantizer.actorder else None
         pieces, r0 = [], 0
         for r in rows:
-            pieces += [qweight[:, r0:r0 + r], scales[:, r0:r0 + r], qzeros[:, r0 * bits // 32:(r0 + r) * bits // 32]]
+            if packed:
+                pieces += [qweight[:, r0:r0 + r], scales[:, r0:r0 + r],
+                           qzeros[:, r0 * bits // 32:(r0 + r) * bits // 32]]
+            else:
+                pieces += [qweight[r0:r0 + r], scales[:, r0:r0 + r], qzeros[:, r0:r0 + r]]
             r0 += r
         perm64 = perm.to(torch.int64) if perm is not None else None
         if qweight.is_cuda:
@@ -165,11 +187,13 @@ class ShardedContext:
         results, r0 = {}, 0
         for i, (m, name, r) in enumerate(zip(modules, names, rows)):
             qw, sc, qz = host[3 * i], host[3 * i + 1], host[3 * i + 2]
+            if gs == -1 and not packed:
+                qz = qz.reshape(r, 1)
             result = GPTQResult(
                 wbits=bits, groupsize=gs, actorder=quantizer.actorder, sym=quantizer.sym,
                 qweight=qw, scales=(sc if gs != -1 else sc.reshape(r, 1)), qzeros=qz,
                 perm=host[3 * len(rows) + i],
-                qweight_is_packed=True, qzeros_is_packed=True, qweight_original_shape=(r, d),
+                qweight_is_packed=packed, qzeros_is_packed=packed, qweight_original_shape=(r, d),
             )
             result.__dict__["_device_dequantized"] = w_hat[r0:r0 + r]
             result.quantization_time = elapsed * r / out_features

@@ -281,6 +281,7 @@ def gptq_quantize(
     q_grid: int = 600,
     q_norm: float = 2.4,
     u_override: Optional[torch.Tensor] = None,
+    perm_override: Optional[torch.Tensor] = None,
 ):
     """GPTQ for one Linear weight [out, d]; ``h`` [d,d] fp32 is modified in place.
 
@@ -302,7 +303,11 @@ def gptq_quantize(
     Returns dict(qweight int32 [out,d], scales fp16 [G,out] or [out,1],
     qzeros int32 [G,out] or [out,1], perm int64 [d] or None, scales_f32 (the
     pre-cast fp32 scales, for tolerance checks), u (the factor used)).
-    ``u_override`` lets a test feed a given U instead of factorising ``h``.
+    ``u_override`` lets a test feed a given U instead of factorising ``h``;
+    ``perm_override`` a given act-order column order instead of torch.argsort's (which
+    is not stable: columns with exactly equal diagonal entries may come in either order,
+    and do on another device or build; a test that found such ties hands over the order
+    it wants both sides to use).
     """
     w = weight.clone().float()
     out, d = w.shape
@@ -315,6 +320,8 @@ def gptq_quantize(
     perm = None
     if actorder:
         perm = torch.argsort(torch.diag(h), descending=True)
+        if perm_override is not None:
+            perm = perm_override.to(perm.dtype)
         w = w[:, perm]
         h = h[perm][:, perm]
         invperm = torch.argsort(perm)

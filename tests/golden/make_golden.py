@@ -277,7 +277,91 @@ def main(ref_root):
              rtn_deq=_np(r["dequantized_weight"]))
     b["rtn_deq_is_bf16"] = np.int64(r["dequantized_weight"].dtype == torch.bfloat16)
     np.savez_compressed(os.path.join(HERE, "bf16.npz"), **b)
+    driver_fixtures(ref_gptq, ref_arch)
     print("golden fixtures written to", HERE)
+
+
+class _FakeModelConfig:
+    """What the reference's driver asks of a ModelConfig: the model and a tokenizer."""
+
+    def __init__(self, model):
+        self._model = model
+
+    def load_model(self, device_map=None):  # pylint: disable=unused-argument
+        return self._model
+
+    def load_tokenizer(self):
+        return None
+
+
+def _run_reference_driver(ref_gptq, ref_arch, model, ids, quantizer_kw, tag, extra=None):
+    """The reference's run_quantize_with_qep_arch (onecomp/qep/_quantize_with_qep_arch.py:323-627)
+    on ``model`` with the token ids ``ids`` on CPU.  Records, in call order, what the driver hands
+    to ``quantize_with_qep`` for every layer (the layer's weight at that moment, H, C or nothing)
+    and every layer's result; layers that took the RTN fallback carry no quantization time."""
+    from onecomp.qep._qep_config import QEPConfig
+
+    original = ref_arch.prepare_calibration_dataset
+    ref_arch.prepare_calibration_dataset = lambda **_kw: {"input_ids": ids}
+    calls = []
+
+    class Recording(ref_gptq.GPTQ):
+        def quantize_with_qep(self, module, quant_input_activation, original_input_activation=None,
+                              percdamp=0.01, perccorr=0.5, hessian=None, delta_hatX=None, nsamples=None):
+            calls.append((self.module_to_name[module], module.weight.data.clone(), hessian.clone(),
+                          None if delta_hatX is None else delta_hatX.clone()))
+            return super().quantize_with_qep(module, quant_input_activation, original_input_activation,
+                                             percdamp=percdamp, perccorr=perccorr, hessian=hessian,
+                                             delta_hatX=delta_hatX, nsamples=nsamples)
+
+    qz = Recording(**quantizer_kw)
+    try:
+        ref_arch.run_quantize_with_qep_arch(
+            model_config=_FakeModelConfig(model), quantizer=qz,
+            qep_config=QEPConfig(device="cpu", percdamp=0.01, perccorr=0.5),
+            calibration_config=None, report_progress=False)
+    finally:
+        ref_arch.prepare_calibration_dataset = original
+    out = {"ids": ids.numpy(), "order": np.array([c[0] for c in calls])}
+    for k, v in (extra or {}).items():
+        out[k] = v
+    for name, p in model.state_dict().items():
+        # the model after the run: target layers hold their dequantized weights
+        out[f"final/{name}"] = _np(p.detach().cpu())
+    for name, w, h, c in calls:
+        # no layer's own weight has changed before its turn
+        assert torch.equal(w, torch.from_numpy(extra[f"init/{name}.weight"].view(np.int16)).view(w.dtype))
+        out[f"H/{name}"] = h.numpy()
+        if c is not None:
+            out[f"C/{name}"] = c.numpy()
+    out["results"] = np.array(list(qz.results))
+    for name, r in qz.results.items():
+        out[f"qweight/{name}"] = r.qweight.numpy()
+        out[f"qzeros/{name}"] = _np(r.qzeros)
+        out[f"scales/{name}"] = _np(r.scales)
+        out[f"packed/{name}"] = np.int64(bool(r.qweight_is_packed))
+        out[f"rtn/{name}"] = np.int64(r.quantization_time is None)
+        if r.perm is not None:
+            out[f"perm/{name}"] = r.perm.numpy()
+    np.savez_compressed(os.path.join(HERE, f"driver_{tag}.npz"), **out)
+
+
+def driver_fixtures(ref_gptq, ref_arch):
+    """Block-wise QEP driver of the reference on the seeded toy models of tests/toy_models.py."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    import toy_models
+
+    torch.set_num_threads(1)
+    for tag, kw in (("llama_b4", dict(wbits=4, groupsize=32, sym=False)),
+                    ("llama_b3_actorder", dict(wbits=3, groupsize=32, sym=True, actorder=True))):
+        model = toy_models.tiny_llama(seed=0)
+        init = {f"init/{k}": _np(v.detach().clone()) for k, v in model.state_dict().items()}
+        _run_reference_driver(ref_gptq, ref_arch, model, toy_models.llama_ids(0), kw, tag, extra=init)
+    model = toy_models.routed_moe(seed=0)
+    init = {f"init/{k}": _np(v.detach().clone()) for k, v in model.state_dict().items()}
+    _run_reference_driver(ref_gptq, ref_arch, model, toy_models.moe_ids(0),
+                          dict(wbits=4, groupsize=16, sym=False, exclude_layer_keywords=["router"]),
+                          "moe", extra=init)
 
 
 def _prep_h(h, perm):

@@ -113,6 +113,72 @@ def test_qep_layer_matches_reference_vectors():
     assert (_codes(r) == want).mean() >= 0.999
 
 
+def test_generic_moments_match_reference_vectors():
+    """Quantizer.calculate_hessian / calculate_delta_hatX (slices of 8 sequences, reference
+    _quantizer.py:764-895) on the reference's own vectors."""
+    from onecompression_b200 import GPTQ
+
+    g = load_golden("moments.npz")
+    xq, xf = f16(g["xq"]).to(DEV), f16(g["xf"]).to(DEV)
+    assert xq.dim() == 3 and xq.shape[0] == 20            # slices of 8, 8 and 4 sequences
+    lin = torch.nn.Linear(64, 8, bias=False).half().to(DEV)
+    q = GPTQ(wbits=4, groupsize=-1)
+    h, n = q.calculate_hessian(lin, xq)
+    c = q.calculate_delta_hatX(lin, xq, xf)
+    assert n == int(g["n"])
+    assert h.is_cuda and c.is_cuda and c.dtype == torch.float32 and c.shape == (64, 64)
+    rel = lambda a, b: ((a.double() - b.double()).norm() / b.double().norm()).item()  # noqa: E731
+    assert rel(h.cpu(), torch.from_numpy(g["H"])) < 1e-5
+    assert rel(c.cpu(), torch.from_numpy(g["C_generic"])) < 1e-5
+    # a 2-D input is one sequence
+    h2, n2 = q.calculate_hessian(lin, xq[0])
+    assert n2 == xq.shape[1] and h2.shape == (64, 64)
+
+
+@pytest.mark.parametrize("bad,attempts", [(-0.015, 2), (-0.5, 3)])
+def test_adjust_weight_escalates_damping_like_the_reference(monkeypatch, bad, attempts):
+    """A Hessian that is not positive definite through adjust_weight (the reference's
+    tests/onecomp/test_qep_damping.py): the correction retries with the reference's damping
+    sequence (damp recomputed from the already damped matrix, 10^k times it added after the k-th
+    failure, _quantizer.py:402-428) and lands on the oracle's corrected weight."""
+    from onecompression_b200 import GPTQ, kernels
+
+    g = torch.Generator().manual_seed(31)
+    d, out = 64, 32
+    h = torch.eye(d)
+    h[5, 5] = bad
+    h[0, 1] = h[1, 0] = 0.3
+    w = (torch.randn(out, d, generator=g) * 0.05).half()
+    c = 0.05 * torch.randn(d, d, generator=g)
+    seen = []
+    original = kernels.factor_hessian
+
+    def spy(*a, **kw):
+        fac = original(*a, **kw)
+        seen.append(fac.attempts)
+        return fac
+
+    monkeypatch.setattr(kernels, "factor_hessian", spy)
+    lin = torch.nn.Linear(d, out, bias=False).half()
+    lin.weight.data = w.clone()
+    lin = lin.to(DEV)
+    q = GPTQ(wbits=4, groupsize=32)
+    q.module_to_name = {lin: "layer"}
+    q.adjust_weight(lin, None, None, original_hessian=h.to(DEV), original_delta_hatX=c.to(DEV),
+                    percdamp=0.01, perccorr=0.5)
+    assert seen == [attempts]
+    want = orc.qep_adjust_weight(w, h, c, 0.01, 0.5)          # the reference's loop, retries included
+    got = lin.weight.data.cpu()
+    ulps = np.abs(got.numpy().view(np.int16).astype(np.int64) - want.numpy().view(np.int16).astype(np.int64))
+    assert ulps.max() <= 1 and (ulps == 0).mean() >= 0.995, (ulps.max(), (ulps == 0).mean())
+    # first attempt fine: exactly one factorisation, no retry
+    seen.clear()
+    lin.weight.data = w.clone().to(DEV)
+    q.adjust_weight(lin, None, None, original_hessian=torch.eye(d, device=DEV),
+                    original_delta_hatX=torch.zeros(d, d, device=DEV))
+    assert seen == [1] and torch.equal(lin.weight.data.cpu(), w)
+
+
 class _Recorder:
     """Mixin that keeps (H, C, W before) of every layer the driver hands over."""
 
@@ -159,6 +225,7 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act, dtype):
     rel = ((inps_q.float() - inps_f.float()).norm() / inps_f.float().norm()).item()
     assert 0 < rel < 0.5
     matched = total = 0
+    perm_differs = []
     for name, (h, c, w_before) in q.inputs.items():
         r = q.results[name]
         i = int(name.split(".")[2])
@@ -171,7 +238,10 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act, dtype):
             w_adj = orc.qep_adjust_weight(w_before, h, c, 0.01, 0.5)
         ref = orc.gptq_quantize(w_adj, h.clone(), wbits=bits, groupsize=gs, sym=sym, actorder=act)
         if act and not np.array_equal(ref["perm"].numpy(), r.perm.numpy()):
-            continue   # a near-tie in diag(H) ordered differently: codes are not comparable
+            # a near-tie in diag(H) ordered differently (torch.argsort is not stable): the codes of
+            # such a layer are not comparable position by position; counted and bounded below
+            perm_differs.append(name)
+            continue
         eq = _codes(r) == ref["qweight"].numpy()
         matched += int(eq.sum())
         total += eq.size
@@ -182,6 +252,8 @@ def test_block_driver_layers_match_oracle(bits, gs, sym, act, dtype):
         mod = dict(stack.blocks[i].named_modules())[name.split(".", 3)[3]]
         assert mod.weight.dtype == dtype
         assert torch.equal(mod.weight.data.cpu(), r.compute_dequantized_weight().to(dtype))
+    print(f"layers whose column order differs from the oracle's: {len(perm_differs)} of {len(q.inputs)} {perm_differs}")
+    assert len(perm_differs) <= 2, perm_differs
     assert total > 0 and matched / total >= 0.999, f"{matched / total:.5f} identical codes over all layers"
 
 

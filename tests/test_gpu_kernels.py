@@ -192,6 +192,75 @@ def test_cross_term_tensor_core_vs_float64(K, engine):
     assert _rel(c.cpu(), want_c) < 1e-4
 
 
+@pytest.mark.parametrize("engine", ["single", "pair", "simt"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_cross_term_when_the_activations_have_drifted_apart(K, engine, dtype):
+    """After many quantized blocks Xq is no small perturbation of Xf: half the magnitude off, signs
+    flipped, tiny entries next to large ones.  fp16(Xf - Xq) alone then carries 2^-11 relative
+    error per element; the kernel carries the difference as two 16-bit terms, so C still meets the
+    bar of H (1e-5 relative Frobenius against float64) for fp16.  bf16 has 8-bit terms: two of
+    them hold 16 bits, which bounds the error at 2^-17 per element."""
+    g = torch.Generator().manual_seed(17)
+    d, ntok = 640, 6000
+    xf = torch.randn(ntok, d, generator=g)
+    xf[:, 100:164] *= 1e-3                                   # a block of tiny entries
+    xf[:, 7] *= 30                                           # an outlier channel
+    xq = xf * (1 + 0.5 * torch.randn(ntok, d, generator=g))
+    flip = torch.rand(ntok, d, generator=g) < 0.1
+    xq = torch.where(flip, -xq, xq)
+    xf, xq = xf.to(dtype), xq.to(dtype)
+    want_c = (2.0 / ntok) * ((xf.double() - xq.double()).t() @ xq.double())
+    want_h = (2.0 / ntok) * (xq.double().t() @ xq.double())
+    acc = K.MomentAccumulator(d, dev(), cross=True, engine=engine)
+    for a, b in zip(xq.to(dev()).split(2500), xf.to(dev()).split(2500)):
+        acc.add(a, b)
+    h, c, n = acc.finalize()
+    assert n == ntok
+    assert _rel(h.cpu(), want_h) < 1e-5
+    bar = 1e-5 if dtype == torch.float16 else 3e-5
+    assert _rel(c.cpu(), want_c) < bar, _rel(c.cpu(), want_c)
+    # C is dominated by its diagonal here (Xf - Xq correlates with Xq), which hides rounding errors
+    # of the difference in a whole-matrix norm; the off-diagonal entries show them.  One 16-bit term
+    # leaves 2e-4 (fp16) / 2e-3 (bf16) there, two terms leave the accumulation error only.
+    off = ~torch.eye(d, dtype=torch.bool)
+    one_term = (2.0 / ntok) * ((xf.float() - xq.float()).to(dtype).double().t() @ xq.double())
+    e_one = _rel(one_term[off], want_c[off])
+    e_two = _rel(c.cpu().double()[off], want_c[off])
+    print(f"[cross {engine} {dtype}] off-diagonal error: two terms {e_two:.2e}, one term would leave {e_one:.2e}")
+    assert e_one > 1e-4
+    assert e_two < 0.1 * e_one and e_two < 3e-5, (e_two, e_one)
+
+
+@pytest.mark.parametrize("cross", [False, True])
+def test_moments_from_strided_activations(K, cross):
+    """Column slices of a wider buffer (row stride 2d) and differently strided Xf / Xq: the result is
+    that of contiguous copies, and nothing beyond the slices is read or written (canaries)."""
+    g = torch.Generator().manual_seed(23)
+    d, ntok = 256, 3000
+    big_q = torch.randn(ntok, 2 * d, generator=g).half().to(dev())
+    big_f = (big_q.float() * (1 + 0.05 * torch.randn(ntok, 2 * d, generator=g).to(dev()))).half()
+    xq = big_q[:, :d]                      # stride 2d, kept as a view by the accumulator
+    xf = big_f[:, d:]                      # stride 2d at a column offset
+    xf_c = xf.contiguous()                 # stride d: differs from xq's
+    guard = big_q[:, d:].clone()
+    want = K.MomentAccumulator(d, dev(), cross=cross)
+    want.add(xq.contiguous(), xf_c if cross else None)
+    h0, c0, _ = want.finalize()
+    for xf_in in ((xf, xf_c) if cross else (None,)):
+        acc = K.MomentAccumulator(d, dev(), cross=cross)
+        acc.add(xq, xf_in)
+        h, c, n = acc.finalize()
+        assert n == ntok and torch.equal(h, h0)
+        if cross:
+            assert torch.equal(c, c0)
+    assert torch.equal(big_q[:, d:], guard)
+    ref_h = (2.0 / ntok) * (xq.double().t() @ xq.double())
+    assert _rel(h0.cpu(), ref_h.cpu()) < 1e-5
+    if cross:
+        ref_c = (2.0 / ntok) * ((xf.double() - xq.double()).t() @ xq.double())
+        assert _rel(c0.cpu(), ref_c.cpu()) < 1e-5
+
+
 # ---- inverse-Hessian factor ---------------------------------------------------------------
 
 @pytest.mark.parametrize("name", gptq_case_names())
@@ -450,3 +519,26 @@ def test_bf16_layer_matches_reference_vectors(K):
     rt = K.rtn_quantize(w, 4, 32, False)
     assert np.array_equal(rt["codes"].cpu().numpy(), g["rtn_codes"])
     assert rt["dequantized"].dtype == torch.bfloat16 and np.array_equal(bits16(rt["dequantized"]), g["rtn_deq"])
+
+
+def test_all_zero_weight_rows_through_the_column_loop(K):
+    """Rows of W that are entirely zero (pruned outputs): find_params gives them the range (-1, +1)
+    (reference _gptq.py:914-917), every code is the zero point, the dequantized row is zero."""
+    g = load_golden("gptq_b4_g128_asym.npz")
+    w = f16(g["W"]).clone()
+    w[3] = 0
+    w[17] = 0
+    h = torch.from_numpy(g["H"])
+    for sym in (False, True):
+        fac = K.factor_hessian(h.to(dev()), 0.01, False)
+        out = K.gptq_quantize(w.to(dev()), fac, wbits=4, groupsize=128, sym=sym, want_codes=True,
+                              want_scales_f32=True)
+        ref = orc.gptq_quantize(w, h.clone(), wbits=4, groupsize=128, sym=sym)
+        codes = out["codes"].cpu().numpy()
+        assert (codes == ref["qweight"].numpy()).mean() >= 0.999
+        for r in (3, 17):
+            assert np.array_equal(codes[r], ref["qweight"].numpy()[r])
+            assert np.array_equal(out["zeros"].cpu().numpy()[:, r], ref["qzeros"].numpy()[:, r])
+            assert torch.equal(out["scales"].cpu()[:, r], ref["scales"][:, r])
+            assert torch.all(out["scales_f32"].cpu()[:, r] == 2.0 / 15.0)
+            assert not out["dequantized"][r].any()

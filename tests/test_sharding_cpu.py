@@ -105,6 +105,25 @@ def _worker(rank, world, port, out_dir):
         assert torch.equal(r.scales, alone["scales"])
         assert torch.equal(r.__dict__["_device_dequantized"], alone["dequantized"])
 
+    # a quantizer that does not pack (bit widths without a packed layout): integer codes and raw
+    # zero points are gathered instead, with the flags of the single-GPU result
+    q5 = GPTQ(wbits=5, groupsize=32, sym=False, bitpack_on_quantize=False)
+    lin5 = torch.nn.Linear(d, out, bias=False).half()
+    lin5.weight.data = w.clone()
+    q5.module_to_name = {lin5: "layer5"}
+
+    def compute_unpacked(w_slab, cross):
+        r = orc.gptq_quantize(w_slab, h_all.clone(), wbits=5, groupsize=32, sym=False, u_override=u)
+        deq = (r["scales"].float().T.repeat_interleave(32, 1)
+               * (r["qweight"].float() - r["qzeros"].float().T.repeat_interleave(32, 1))).half()
+        return {"codes": r["qweight"], "zeros": r["qzeros"], "scales": r["scales"], "dequantized": deq}
+
+    res5 = ctx.quantize_rows(q5, lin5, h_all, None, QEPConfig(), F(), compute=compute_unpacked)
+    whole5 = compute_unpacked(w, None)
+    assert not res5.qweight_is_packed and not res5.qzeros_is_packed
+    assert res5.qweight.shape == (out, d) and torch.equal(res5.qweight, whole5["codes"])
+    assert torch.equal(res5.qzeros, whole5["zeros"]) and torch.equal(res5.scales, whole5["scales"])
+
     # independent layers (experts): dealt round-robin, results broadcast from their owners
     experts, items = [], []
     q3 = GPTQ(wbits=4, groupsize=32, sym=False)
@@ -144,3 +163,54 @@ def test_token_and_row_sharding_two_ranks(tmp_path, world):
     port = _free_port()
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_correction_factor_rule(monkeypatch):
+    """The QEP correction may borrow the column loop's factor only if that factor was built with the
+    correction's damping and needed no retry (reference adjust_weight, _quantizer.py:396-428, damps
+    and retries by its own rule); otherwise the Hessian is factored again, without act-order and
+    with the correction's shift sequence.  One GPU and the row-sharded path share this rule."""
+    from onecompression_b200 import kernels
+    from onecompression_b200.kernels import HessianFactor
+    from onecompression_b200.quantizer import _quantizer as qmod
+
+    calls = []
+
+    def fake_factor(h, percdamp, actorder, max_retries=5, shifts=None):
+        calls.append((percdamp, actorder, shifts is not None))
+        return "fresh"
+
+    monkeypatch.setattr(kernels, "factor_hessian", fake_factor)
+    z = torch.zeros(1)
+
+    def fac(percdamp, attempts, actorder=False):
+        return HessianFactor(z, z, z, z, z, actorder, percdamp, 1.0, attempts)
+
+    same = fac(0.01, 1)
+    assert qmod.qep_factor(None, same, 0.01) is same and not calls
+    act = fac(0.01, 1, actorder=True)
+    assert qmod.qep_factor(None, act, 0.01) is act and not calls          # the kernels apply P
+    assert qmod.qep_factor(None, fac(0.05, 1), 0.01) == "fresh"            # other damping
+    assert qmod.qep_factor(None, fac(0.01, 2), 0.01) == "fresh"            # a retried factor
+    assert qmod.qep_factor(None, None, 0.01) == "fresh"
+    assert calls == [(0.01, False, True)] * 3
+
+    # the shift sequence of the retry rule, in units of the first damp, against the reference's loop:
+    # damp_k = percdamp * mean(diag) of the matrix as damped so far; after the k-th failure
+    # 10^k * damp_k more is added
+    def reference_totals(percdamp, attempts, mean=1.0):
+        total, out, mult = 0.0, [], 1.0
+        for k in range(attempts):
+            damp = percdamp * (mean + total)
+            total += damp
+            out.append(total / (percdamp * mean))
+            mult *= 10.0
+            total += mult * damp          # what the except branch adds before the next attempt
+        return out
+
+    rule = qmod._qep_shift_rule()
+    got = [rule(k, 0.01) for k in range(4)]
+    want = reference_totals(0.01, 4)
+    assert got[0] == 1.0
+    for k in range(4):
+        assert abs(got[k] - want[k]) <= 1e-12 * want[k], (k, got, want)

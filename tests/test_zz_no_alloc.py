@@ -49,7 +49,7 @@ def test_static_scratch_entry_point_matches_regular_one():
         h = torch.zeros(d, d, device=dev)
         c = torch.zeros(d, d, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
-        scratch = torch.empty(t * d, dtype=torch.float16, device=dev)
+        scratch = torch.empty(2 * t * d, dtype=torch.float16, device=dev)
         n = 0
         for xq, xf in chunks:                      # two calls in a row
             assert _accumulate(lib, name, xq, xf, h, c, n, status, scratch) == 0, lib.oc_last_error()
