@@ -308,6 +308,10 @@ def run_ours(args):
     peaks = _peaks()
     achieved = executed / (k_ms * 1e-3) / 1e12
 
+    del stack, host_blocks, acc, xq, xf
+    kernels.release_workspaces()
+    torch.cuda.empty_cache()
+    parity = sharded_parity(ctx, dev) if world > 1 else None
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -324,8 +328,7 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": round(value / PUBLISHED_S, 5), "dtype": "f32",
         "data": "synthetic",
         "config": {
-            "workload": "llama3-8b decoder blocks, QEP(alpha 0.5)+GPTQ 3-bit g128, 128x2048 tokens; "
-                        "1 step = 1 block (7 linears), value = 32 x step",
+            "workload": WORKLOAD,
             "l2": "inputs larger than L2 (4 GiB of activations per step)",
             "parallelism": f"tokens/{world} for H,C + rows/{world} for the column loop" if world > 1 else "single GPU",
             "baseline_note": "published 271.8 s is the reference's sum of per-layer quantize time only "
@@ -349,11 +352,262 @@ def run_ours(args):
             "ms_per_launch": round(k_ms, 4),
         },
     }
+    if parity is not None:
+        line["parity_vs_single"] = parity
+    if world == 1 and not args.skip_extras:
+        del x0
+        torch.cuda.empty_cache()
+        line["other_configs"] = other_configs(dev)
+        line["same_box_torch_ops_ms"] = same_box_torch_ops(dev)
     if world == 1:
-        line["cpu_baseline"] = cpu_baseline(sample_seconds_hint=20)
+        line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------
+# the other configurations and the same-box library baselines (one GPU, outside the timed region)
+# --------------------------------------------------------------------------------------
+
+
+def _timed(fn, reps=1):
+    """Device milliseconds per call of ``fn`` on the current stream (one untimed call first)."""
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def other_configs(dev):
+    """Driver-visible figures for the configurations the main timed region does not run:
+    1: one 4096x4096 layer, 32x2048 tokens, GPTQ 4-bit asym g128 (moments + factor + column loop);
+    2: one Llama-3-8B block, all seven linears GPTQ 4-bit asym g128 act-order from full-precision
+       activations (128x2048 tokens), through the chunked hook path;
+    5: one GPT-OSS-20B-shaped mixture layer: 32 experts of three 2880x2880 linears, per-expert
+       Hessians from top-4 routed tokens with skewed counts (128x2048 tokens), GPTQ 4-bit g32,
+       factorisations and column loops batched over the experts.
+    Times are device milliseconds with the inputs resident in HBM."""
+    from onecompression_b200 import GPTQ, kernels, synthetic
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(1)
+    # ---- configuration 1 ----
+    d = 4096
+    w = (torch.randn(d, d, generator=g, device=dev) * 0.02).half()
+    x = torch.randn(32, SEQ_LEN, d, generator=g, device=dev)
+    x[..., torch.randperm(d, generator=g, device=dev)[:8]] *= 20
+    x = x.half()
+    lin = torch.nn.Linear(d, d, bias=False, device=dev, dtype=torch.float16)
+    lin.weight.data = w
+    q1 = GPTQ(wbits=4, groupsize=128, sym=False)
+    q1.module_to_name = {lin: "layer"}
+
+    def config1():
+        h, _n = q1.calculate_hessian(lin, x)
+        q1.quantize_layer(lin, None, hessian=h)
+
+    out["config1_single_linear_ms"] = round(_timed(config1, 2), 3)
+    del x, w, lin
+    # ---- configuration 2 ----
+    shape = synthetic.LLAMA3_8B
+    stack = synthetic.llama_blocks(shape, 1, SEQ_LEN, dev, seed=2)
+    x0 = synthetic.embedded_tokens(shape["vocab_size"], shape["hidden_size"], N_SEQ, SEQ_LEN, dev, seed=2)
+    blk = stack.blocks[0]
+    pristine = {k: v.clone() for k, v in blk.state_dict().items()}
+
+    class OneBlock(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([blk])
+
+        def forward(self, input_ids, use_cache=False):        # "ids" are the embedded tokens here
+            return blk(input_ids, **stack.kwargs)
+
+    from onecompression_b200.runner_methods.chunked_quantization import run_chunked_quantization
+
+    model = OneBlock()
+
+    def config2():
+        blk.load_state_dict(pristine)
+        q2 = GPTQ(wbits=4, groupsize=128, sym=False, actorder=True)
+        run_chunked_quantization(None, [q2], None, report_progress=False, model=model,
+                                 model_inputs={"input_ids": x0}, batch_size=16)
+
+    out["config2_actorder_block_ms"] = round(_timed(config2, 1), 2)
+    del stack, x0, blk, model, pristine
+    kernels.release_workspaces()
+    torch.cuda.empty_cache()
+    # ---- configuration 5 ----
+    hid, n_exp, top_k, n_tok = 2880, 32, 4, N_SEQ * SEQ_LEN
+    xs = (torch.randn(n_tok, hid, generator=g, device=dev) * 0.5).half()
+    skew = torch.linspace(2.0, -2.0, n_exp, device=dev)                 # popular and rare experts
+    logits = torch.randn(n_tok, n_exp, generator=g, device=dev) + skew
+    choice = logits.topk(top_k, dim=-1).indices
+    experts = []
+    for _e in range(n_exp):
+        mods = {k: torch.nn.Linear(hid, hid, bias=False, device=dev, dtype=torch.float16) for k in ("gate", "up", "down")}
+        for m in mods.values():
+            m.weight.data.normal_(0.0, 0.02, generator=g)
+        experts.append(mods)
+    q5 = GPTQ(wbits=4, groupsize=32, sym=False)
+    for e, mods in enumerate(experts):
+        for k, m in mods.items():
+            q5.module_to_name[m] = f"model.layers.0.mlp.experts.{e}.{k}_proj"
+    counts = []
+
+    def config5():
+        items = []
+        counts.clear()
+        for e, mods in enumerate(experts):
+            rows = torch.nonzero((choice == e).any(dim=-1)).flatten()
+            counts.append(int(rows.numel()))
+            xe = xs[rows]
+            acc = kernels.MomentAccumulator(hid, dev)
+            acc.add(xe)
+            h_in, _c, _n = acc.finalize(check=False)
+            mid = torch.nn.functional.silu(mods["gate"](xe)) * mods["up"](xe)
+            acc2 = kernels.MomentAccumulator(hid, dev)
+            acc2.add(mid)
+            h_mid, _c, _n = acc2.finalize(check=False)
+            items += [(mods["gate"], h_in), (mods["up"], h_in), (mods["down"], h_mid)]
+        q5.quantize_independent(items)
+
+    with torch.no_grad():
+        out["config5_moe_layer_96_linears_ms"] = round(_timed(config5, 1), 2)
+    out["config5_tokens_per_expert_min_max"] = [min(counts), max(counts)]
+    return out
+
+
+def same_box_torch_ops(dev):
+    """What the reference's own torch calls cost on this GPU for the pieces the kernels replace
+    (milliseconds, each beside the kernel that replaces it): the fp32 cast + SGEMM of the Hessian
+    (onecomp/quantizer/_quantizer.py:824-830), potrf + potri + potrf
+    (onecomp/quantizer/gptq/_gptq.py:618-643), the potrf + potrs correction
+    (_quantizer.py:22-31, 407-412) and the per-block SGEMM of the lazy-batch update (_gptq.py:765)."""
+    from onecompression_b200 import kernels
+
+    table = {}
+    g = torch.Generator(device=dev).manual_seed(3)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for d, ntok in ((4096, 16384), (14336, 16384)):
+            x = torch.randn(ntok, d, generator=g, device=dev).half()
+            x[:, ::97] *= 8
+            h_t = torch.zeros(d, d, device=dev)
+
+            def torch_h():
+                xs = x.float() * (2.0 / ntok) ** 0.5
+                h_t.addmm_(xs.t(), xs)
+
+            acc = kernels.MomentAccumulator(d, dev)
+            table[f"hessian_d{d}_{ntok}tok"] = {"torch_cast_sgemm": round(_timed(torch_h, 2), 3),
+                                                "moment_tc_kernel": round(_timed(lambda: acc.add(x), 2), 3)}
+            h, _c, _n = acc.finalize()       # the running mean over repeated tokens is the tokens' own moment
+            del x, h_t
+            fac = kernels.factor_hessian(h, PERCDAMP, False)
+            damp = float(fac.damp[0])
+
+            def torch_factor():
+                hh = h.clone()
+                hh.diagonal().add_(damp)
+                low = torch.linalg.cholesky(hh)
+                return torch.linalg.cholesky(torch.cholesky_inverse(low), upper=True)
+
+            table[f"inverse_factor_d{d}"] = {
+                "torch_potrf_potri_potrf": round(_timed(torch_factor, 2), 3),
+                "oc_hinv_factor": round(_timed(lambda: kernels.factor_hessian(h, PERCDAMP, False), 2), 3)}
+            out_f = 4096
+            w = (torch.randn(out_f, d, generator=g, device=dev) * 0.02).half()
+            c = (0.01 * h + 0.001).contiguous()
+
+            def torch_qep():
+                hh = h.clone()
+                hh.diagonal().add_(damp)
+                rhs = w.float() @ c
+                low = torch.linalg.cholesky(hh)
+                return (w.float() + PERCCORR * torch.cholesky_solve(rhs.t(), low).t()).half()
+
+            w2 = w.clone()
+            table[f"qep_correction_{out_f}x{d}"] = {
+                "torch_sgemm_potrf_potrs": round(_timed(torch_qep, 2), 3),
+                "oc_qep_adjust": round(_timed(lambda: kernels.qep_adjust(w2, c, fac, PERCCORR), 2), 3)}
+            wf = w.float()
+            err = torch.randn(out_f, 128, generator=g, device=dev) * 1e-3
+            u = fac.u
+
+            def torch_trailing():
+                for i1 in range(0, d - 128, 128):
+                    wf[:, i1 + 128:].sub_(err @ u[i1:i1 + 128, i1 + 128:])
+
+            table[f"column_loop_{out_f}x{d}"] = {
+                "torch_trailing_sgemms_only": round(_timed(torch_trailing, 1), 3),
+                "oc_gptq_quantize_whole_loop": round(_timed(
+                    lambda: kernels.gptq_quantize(w, fac, wbits=WBITS, groupsize=GROUPSIZE, sym=True), 2), 3)}
+            del w, w2, wf, c, h, fac, u
+            kernels.release_workspaces()
+            torch.cuda.empty_cache()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    return table
+
+
+def sharded_parity(ctx, dev):
+    """Correctness evidence for the multi-GPU path, outside the timed region: one stacked group
+    (q/k/v shapes, QEP correction + GPTQ) quantized row-sharded over all ranks and again whole on
+    every rank from the same H, C and weights.  Returns the fraction of identical packed words and
+    the largest difference of the fp16 scales in ulps (rows are independent: 1.0 and 0 expected)."""
+    import torch.distributed as dist
+
+    from onecompression_b200 import GPTQ, QEPConfig, kernels
+
+    g = torch.Generator(device=dev).manual_seed(5)          # the same tensors on every rank
+    d = 4096
+    x = torch.randn(8192, d, generator=g, device=dev).half()
+    xf = (x.float() * (1 + 0.03 * torch.randn(x.shape, generator=g, device=dev))).half()
+    acc = kernels.MomentAccumulator(d, dev, cross=True)
+    acc.add(x, xf)
+    h, c, _n = acc.finalize()
+    rows = (4096, 1024, 1024)
+    results = []
+    for sharded in (True, False):
+        mods = []
+        gw = torch.Generator(device=dev).manual_seed(6)
+        q = GPTQ(wbits=WBITS, groupsize=GROUPSIZE, percdamp=PERCDAMP)
+        for i, r in enumerate(rows):
+            m = torch.nn.Linear(d, r, bias=False, device=dev, dtype=torch.float16)
+            m.weight.data.normal_(0.0, 0.02, generator=gw)
+            q.module_to_name[m] = f"model.layers.0.self_attn.{'qkv'[i]}_proj"
+            mods.append(m)
+        fac = kernels.factor_hessian(h, PERCDAMP, False)
+        cfg = QEPConfig(percdamp=PERCDAMP, perccorr=PERCCORR)
+        if sharded:
+            res = ctx.quantize_rows_stacked(q, mods, h, c, cfg, fac)
+        else:
+            res = q.quantize_stacked(mods, h, fac, c, PERCDAMP, PERCCORR)
+        kernels.finish_host_copies()
+        torch.cuda.synchronize()
+        results.append([res[m] for m in mods])
+    same = total = 0
+    ulps = 0
+    for a, b in zip(*results):
+        same += int((a.qweight == b.qweight).sum()) + int((a.qzeros == b.qzeros).sum())
+        total += a.qweight.numel() + a.qzeros.numel()
+        ulps = max(ulps, int((a.scales.view(torch.int16).int() - b.scales.view(torch.int16).int()).abs().max()))
+    counts = torch.tensor([same, total], dtype=torch.int64, device=dev)
+    worst = torch.tensor([ulps], dtype=torch.int64, device=dev)
+    dist.all_reduce(counts)                                  # every rank holds the full result: all must agree
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"identical_packed_words": round(counts[0].item() / max(1, counts[1].item()), 6),
+            "max_scale_ulps": int(worst.item()),
+            "what": "q/k/v-shaped stacked group (6144x4096), QEP + GPTQ 3-bit g128: row-sharded over the ranks "
+                    "vs whole on one GPU, same H, C, W"}
 
 
 # --------------------------------------------------------------------------------------
@@ -361,50 +615,95 @@ def run_ours(args):
 # --------------------------------------------------------------------------------------
 
 
-def _cpu_sample(tokens: int, out: int, d: int):
-    """One QEP-GPTQ layer on the CPU oracle: moments over ``tokens`` tokens, correction,
-    GPTQ 3-bit g128.  Returns seconds per phase."""
+LLAMA_LINEARS = [("q_proj", 4096, 4096, True), ("k_proj", 1024, 4096, True), ("v_proj", 1024, 4096, True),
+                 ("o_proj", 4096, 4096, True), ("gate_proj", 14336, 4096, True), ("up_proj", 14336, 4096, True),
+                 ("down_proj", 4096, 14336, False)]          # (name, out, in, corrected by QEP)
+WORKLOAD = ("llama3-8b decoder blocks, QEP(alpha 0.5)+GPTQ 3-bit g128, 128x2048 tokens; "
+            "1 step = 1 block (7 linears), value = 32 x step")
+
+
+def _cpu_moments(tokens: int, d: int, cross: bool):
+    """Seconds for H (and C) of ``tokens`` tokens at width ``d`` on the CPU oracle, plus H."""
     from oracle import gptq_oracle as orc
 
-    g = torch.Generator().manual_seed(0)
-    w = (torch.randn(out, d, generator=g) * 0.02).half()
+    g = torch.Generator().manual_seed(d)
     xf = torch.randn(tokens // SEQ_LEN, SEQ_LEN, d, generator=g).half()
     xq = (xf.float() * (1 + 0.02 * torch.randn(xf.shape, generator=g))).half()
     t0 = time.time()
-    h, c, n = orc.hessian_and_crossterm(xq.split(16), xf.split(16))
+    if cross:
+        h, c, _n = orc.hessian_and_crossterm(xq.split(16), xf.split(16))
+    else:
+        h, c, _n = orc.hessian_and_crossterm(xq.split(16))
+    return time.time() - t0, h, c
+
+
+def _cpu_layer(out: int, d: int, h, c, rows=None):
+    """Seconds (correction, factorisation, column loop) for one layer on the CPU oracle as the
+    reference runs it: QEP correction (potrf + potrs, when ``c`` is given) and GPTQ 3-bit g128
+    (potrf + potri + potrf, then the column loop).  With ``rows`` only that many rows go through
+    (rows are independent; the factorisations are whole)."""
+    from oracle import gptq_oracle as orc
+
+    g = torch.Generator().manual_seed(out + d)
+    w = (torch.randn(rows or out, d, generator=g) * 0.02).half()
+    t0 = time.time()
+    if c is not None:
+        w = orc.qep_adjust_weight(w, h, c, PERCDAMP, PERCCORR)
     t1 = time.time()
-    wa = orc.qep_adjust_weight(w, h, c, PERCDAMP, PERCCORR)
+    hd = h.clone()
+    dead = torch.diag(hd) == 0
+    hd[dead, dead] = 1
+    u = orc.inverse_hessian_upper(hd, PERCDAMP)          # the same call gptq_quantize makes
     t2 = time.time()
-    orc.gptq_quantize(wa, h.clone(), wbits=WBITS, groupsize=GROUPSIZE, sym=True, percdamp=PERCDAMP)
-    t3 = time.time()
-    return {"moments": t1 - t0, "adjust": t2 - t1, "gptq": t3 - t2}
+    orc.gptq_quantize(w, h.clone(), wbits=WBITS, groupsize=GROUPSIZE, sym=True, percdamp=PERCDAMP, u_override=u)
+    return t1 - t0, t2 - t1, time.time() - t2
 
 
-def _extrapolate(sample, tokens, out, d):
-    """Whole-model seconds from one sampled layer, scaling each phase by its FLOP count:
-    moments ~ N d² per group (4 groups: 3 of d=4096 with C, 1 of d=14336 without),
-    correction and GPTQ ~ out d² (plus d³ factorisations) per layer."""
+def cpu_block_sample(tokens: int, full_rows: bool):
+    """One decoder block's quantizer work on the host cores with the CPU restatement of the
+    reference: the moments of the four input-sharing groups on ``tokens`` tokens, then the seven
+    linears at their real widths, each with its own factorisations as the reference does them
+    (incl. the three at d = 14336 and the 4096 x 14336 column loop).  ``full_rows`` False runs the
+    column loops of the widest layers on a row subset and scales them by rows (stated in the
+    sample text).  Block forward passes are not included.  Returns (seconds by phase, text)."""
     n_total = N_SEQ * SEQ_LEN
-    mom_unit = sample["moments"] / (2 * tokens * d * d)          # H and C
-    mom = mom_unit * n_total * (3 * 2 * 4096 ** 2 + 14336 ** 2)
-    layers = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
-    adj_unit = sample["adjust"] / (2 * out * d * d + d ** 3)
-    gptq_unit = sample["gptq"] / (out * d * d + d ** 3)
-    adj = sum(adj_unit * (2 * o * i * i + i ** 3) for o, i in layers[:-1])
-    gq = sum(gptq_unit * (o * i * i + i ** 3) for o, i in layers)
-    return MODEL_LAYERS * (mom + adj + gq)
+    phases = {"moments": 0.0, "correction": 0.0, "gptq": 0.0}
+    t_m, h4, c4 = _cpu_moments(tokens, 4096, True)
+    phases["moments"] += 3 * t_m                   # q/k/v, o and gate/up groups: H and C at d = 4096
+    t_m2, h14, _ = _cpu_moments(tokens, 14336, False)
+    phases["moments"] += t_m2                      # down_proj: H only
+    scaled = []
+    measured = phases["moments"] - 2 * t_m           # what actually ran: one d = 4096 sample, one d = 14336
+    for name, out, d, corrected in LLAMA_LINEARS:
+        h = h4 if d == 4096 else h14
+        c = c4 if corrected else None
+        rows = None
+        if not full_rows and out * d > 4096 * 4096:
+            rows = 1024
+        t_c, t_f, t_l = _cpu_layer(out, d, h, c, rows)
+        measured += t_c + t_f + t_l
+        if rows:
+            # the factorisations are whole; the products and the column loop go with the rows
+            t_l *= out / rows
+            t_c *= out / rows
+            scaled.append(name)
+        phases["correction"] += t_c
+        phases["gptq"] += t_f + t_l
+    block = phases["moments"] * n_total / tokens + phases["correction"] + phases["gptq"]
+    text = (f"one full decoder block on the CPU restatement of the reference: moments of the 4 groups on "
+            f"{tokens} of {n_total} tokens {phases['moments']:.1f}s (scaled to all tokens), 6 corrections "
+            f"{phases['correction']:.1f}s, 7 GPTQ layers at their real widths {phases['gptq']:.1f}s"
+            + (f" (column loops of {', '.join(scaled)} on 1024 rows, scaled by rows)" if scaled else "")
+            + "; x 32 blocks; block forward passes not included")
+    return phases, measured, block * MODEL_LAYERS, text
 
 
-def cpu_baseline(sample_seconds_hint=20):
-    tokens, out, d = 4 * SEQ_LEN, 4096, 4096
-    s = _cpu_sample(tokens, out, d)
-    return {
-        "value": round(_extrapolate(s, tokens, out, d), 1), "unit": "s",
-        "cores": torch.get_num_threads(), "kind": "port",
-        "sample": f"one 4096x4096 layer, {tokens} of {N_SEQ * SEQ_LEN} tokens: moments {s['moments']:.2f}s, "
-                  f"correction {s['adjust']:.2f}s, GPTQ {s['gptq']:.2f}s; scaled to 32 blocks by FLOP count "
-                  "(block forward passes not included)",
-    }
+def cpu_baseline():
+    """The bounded CPU sample that travels with this package's line (about 20-30 s): a 2048-token
+    moment sample and row subsets of the widest layers."""
+    _phases, measured, value, text = cpu_block_sample(tokens=SEQ_LEN, full_rows=False)
+    return {"value": round(value, 1), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
+            "measured_s": round(measured, 1), "sample": text}
 
 
 def run_reference(args):
@@ -416,29 +715,22 @@ def run_reference(args):
         # cores a single process would get (one thread per physical core, as torch's default)
         n = os.cpu_count() or 1
         torch.set_num_threads(max(1, min(32, n // 2 if n > 16 else n)))
-    tokens, out, d = 4 * SEQ_LEN, 4096, 4096
-    for _ in range(min(args.warmup, 1)):
-        _cpu_sample(SEQ_LEN, 1024, 1024)
-    vals = []
-    samples = []
-    for _ in range(max(1, min(args.steps, 3))):
-        s = _cpu_sample(tokens, out, d)
-        samples.append(s)
-        vals.append(_extrapolate(s, tokens, out, d))
-    value = sum(vals) / len(vals)
-    s = samples[-1]
-    sample = (f"one 4096x4096 layer per step, {tokens} of {N_SEQ * SEQ_LEN} tokens: moments {s['moments']:.2f}s, "
-              f"correction {s['adjust']:.2f}s, GPTQ {s['gptq']:.2f}s; scaled to 32 blocks by FLOP count "
-              "(block forward passes not included)")
+    if args.warmup > 0:
+        _cpu_layer(1024, 1024, _cpu_moments(SEQ_LEN, 1024, False)[1], None)      # library warm-up only
+    # one step = one full block, every layer at its real shape and row count
+    t0 = time.time()
+    _phases, measured, value, text = cpu_block_sample(tokens=2 * SEQ_LEN, full_rows=True)
+    wall = time.time() - t0
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 1), "unit": "s",
-        "n_gpus": args.gpus, "steps": len(vals), "warmup": min(args.warmup, 1),
-        "ms_per_step": round(value / MODEL_LAYERS * 1e3, 1), "higher_is_better": False,
+        "n_gpus": args.gpus, "steps": 1, "warmup": min(args.warmup, 1),
+        "ms_per_step": round(wall * 1e3, 1), "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama3-8b decoder blocks, QEP(alpha 0.5)+GPTQ 3-bit g128, 128x2048 tokens; "
-                               "CPU restatement of the reference on the host cores"},
+        "config": {"workload": WORKLOAD,
+                   "arm": "CPU restatement of the reference on the host cores; ms_per_step is the measured "
+                          "wall time of the sampled block, value the whole model"},
         "cpu_baseline": {"value": round(value, 1), "unit": "s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+                         "kind": "port", "measured_s": round(measured, 1), "sample": text},
         "e2e": {"value": round(value, 1), "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -485,6 +777,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--verbose", action="store_true", help="per-step memory figures on stderr")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="leave out the other configurations and the same-box library baselines")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="profiling aid: leave out the host-buffer pass (the line then has no e2e value)")
     ap.add_argument("--profile-case", default=None, choices=["moment", "column", "factor", "qep"],

@@ -5,8 +5,11 @@
 // Cholesky factorisation and one triangular inverse:
 //
 //   A = J (P H P^T + damp I) J      (J reverses the index order, P is the act-order permutation)
-//   A = L L^T                       blocked right-looking Cholesky (two levels: 128 / 512), fp32
-//   X = L^-1                        recursive blocked triangular inverse, fp32
+//   A = L L^T                       blocked right-looking Cholesky (two levels: 128 / 512), fp32:
+//                                   diagonal block on one SM, panel solve by forward substitution
+//                                   (fp32 FMAs, all SMs), updates on the tensor cores (3xTF32)
+//   X = L^-1                        diagonal blocks inverted in one launch, then joined level by
+//                                   level (recursive blocked triangular inverse), fp32
 //   U = J X J                       upper triangular, U^T U = (P H P^T + damp I)^-1
 //
 // because J L J is the upper factor V of H = V V^T and U = V^-1.
@@ -113,46 +116,58 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
   U[(long long)i * ldu + j] = (j >= i) ? X[(long long)(n - 1 - i) * ldx + (n - 1 - j)] : 0.f;
 }
 
-// ---- one diagonal block: Cholesky and inverse of a (<=128)^2 block on one SM -----------------
-// A block (nb x nb, lower part read) -> L written back over the lower part;
-// L^-1 written to the matching block of X (lower part; upper part zero).
+// ---- one diagonal block: Cholesky of a (<=128)^2 block on one SM ----------------------------
+// A block (nb x nb, lower part read) -> L written back over the lower part, L^T over the upper.
 // A non-positive or non-finite pivot records (global index + 1) in *status (first one wins)
 // and continues with pivot 1 so that every later kernel still terminates.
 //
-// Factorisation: 16 x 16 threads, each holding an 8 x 8 sub-block in registers.  The eight
-// columns of a micro-panel are finished inside the one warp that holds that block column
-// (shuffles only), published to shared memory, and every thread to the right applies them as
-// eight rank-1 updates to its registers: one barrier per eight columns.  Inverse: the 8 x 8
-// diagonal blocks are inverted at once, then neighbouring inverted blocks are joined level by
-// level (four levels, two small products each).
-__global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, long long lda,
-                                                         float* __restrict__ X, long long ldx,
-                                                         int k0, int nb, int* __restrict__ status,
-                                                         long long sW) {
+// 16 x 16 threads, each holding an 8 x 8 sub-block in registers.  The eight columns of a
+// micro-panel are finished inside the one warp that holds that block column (shuffles only),
+// published to shared memory, and every thread to the right applies them as eight rank-1 updates
+// to its registers: one barrier per eight columns.
+constexpr int POTRF_SMEM = (NB * (NB + 4) + 2 * 8 * (NB + 4)) * (int)sizeof(float);
+__global__ void __launch_bounds__(256) potrf_block_kernel(float* __restrict__ A, long long lda, int k0, int nb,
+                                                          int* __restrict__ status, long long sW) {
   A += (long long)blockIdx.x * sW;
-  X += (long long)blockIdx.x * sW;
   status += blockIdx.x;
   extern __shared__ __align__(16) float sm[];
-  float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
-  float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
-  float* T = sm + 2 * NB * (NB + 1);                                               // [64 * 64]
+  // The block travels between global memory and the register blocks through shared memory, so
+  // that global accesses are whole rows.  Row r of the block sits at staging row (r % 8) * 16 + r / 8:
+  // the sixteen threads of a block column then read sixteen consecutive staging rows at once.
+  float (*St)[NB + 4] = reinterpret_cast<float (*)[NB + 4]>(sm);
+  // L of the current 8-column micro-panel, column-major [8][128], double buffered
+  float (*Lp)[8][NB + 4] = reinterpret_cast<float (*)[8][NB + 4]>(sm + NB * (NB + 4));
   // block column tx of the 16 x 16 grid of 8 x 8 register blocks lives in one half-warp
   const int tid = threadIdx.x, tx = tid >> 4, ty = tid & 15;
   const int r0 = ty * 8, c0 = tx * 8;
   float* Ab = A + (long long)k0 * lda + k0;
-  float* Xb = X + (long long)k0 * ldx + k0;
-  // L of the current 8-column micro-panel, column-major [8][128], double buffered; it overlays
-  // Y, which is not used before the inverse phase
-  float (*Lp)[8][NB + 4] = reinterpret_cast<float (*)[8][NB + 4]>(&Y[0][0]);
 
+  if (nb == NB) {
+#pragma unroll
+    for (int it = 0; it < NB * NB / 4 / 256; ++it) {
+      const int e = it * 256 + tid, r = e / (NB / 4), c4 = e % (NB / 4);
+      *reinterpret_cast<float4*>(&St[(r & 7) * 16 + (r >> 3)][4 * c4]) =
+          *reinterpret_cast<const float4*>(Ab + (long long)r * lda + 4 * c4);
+    }
+  } else {
+    for (int e = tid; e < NB * NB; e += 256) {
+      const int r = e / NB, c = e % NB;
+      St[(r & 7) * 16 + (r >> 3)][c] = (r < nb && c < nb) ? Ab[(long long)r * lda + c] : 0.f;
+    }
+  }
+  __syncthreads();
   float a[8][8];
 #pragma unroll
-  for (int ii = 0; ii < 8; ++ii)
+  for (int ii = 0; ii < 8; ++ii) {
+    const float4 lo = *reinterpret_cast<const float4*>(&St[ii * 16 + ty][c0]);
+    const float4 hi = *reinterpret_cast<const float4*>(&St[ii * 16 + ty][c0 + 4]);
+    const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
     for (int cc = 0; cc < 8; ++cc) {
       const int r = r0 + ii, c = c0 + cc;
-      a[ii][cc] = (r < nb && c <= r) ? Ab[(long long)r * lda + c] : ((r == c) ? 1.f : 0.f);
+      a[ii][cc] = (r < nb && c <= r) ? v[cc] : ((r == c) ? 1.f : 0.f);
     }
+  }
 
   for (int jb = 0; jb < NB / 8; ++jb) {
     const int buf = jb & 1;
@@ -217,20 +232,140 @@ __global__ void __launch_bounds__(256) potrf_diag_kernel(float* __restrict__ A, 
       }
     }
   }
-  __syncthreads();          // Lp overlays Y: everyone is done with it before S / Y are written
-#pragma unroll
-  for (int ii = 0; ii < 8; ++ii)
-#pragma unroll
-    for (int cc = 0; cc < 8; ++cc) {
-      const int r = r0 + ii, c = c0 + cc;
-      S[r][c] = (c <= r) ? a[ii][cc] : 0.f;
-      if (r < nb && c <= r) Ab[(long long)r * lda + c] = a[ii][cc];
-    }
+  // L goes back over the lower part and, transposed, over the upper part (nothing reads the upper
+  // part of a diagonal block of A as matrix data; the panel solve loads L^T from there)
   __syncthreads();
+#pragma unroll
+  for (int ii = 0; ii < 8; ++ii) {
+    float v[8];
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) v[cc] = (c0 + cc <= r0 + ii) ? a[ii][cc] : 0.f;
+    *reinterpret_cast<float4*>(&St[ii * 16 + ty][c0]) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(&St[ii * 16 + ty][c0 + 4]) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  __syncthreads();
+  // row r of the result: L[r][c] for c <= r, L[c][r] for c > r
+  for (int e = tid; e < NB * NB; e += 256) {
+    const int r = e / NB, c = e % NB;
+    if (r < nb && c < nb) {
+      const int hi = max(r, c), lo = min(r, c);
+      Ab[(long long)r * lda + c] = St[(hi & 7) * 16 + (hi >> 3)][lo];
+    }
+  }
+}
 
-  // ---- inverse of L by doubling: the sixteen 8 x 8 diagonal blocks at once, then four levels
-  // that join neighbouring inverted blocks of size s:  X21 = -X22 (L21 X11) ----
-  for (int e = tid; e < NB * (NB + 1); e += 256) (&Y[0][0])[e] = 0.f;
+// ---- panel solve: P <- P * L^-T for the rows below a factored diagonal block -----------------
+// L = the 128 x 128 lower block at (k0, k0), P = the `rest` rows below it (same columns).  Row r of
+// the result is the forward substitution y_j = (p_j - sum_{i<j} y_i L[j][i]) / L[j][j]: rows are
+// independent.  A CTA takes 128 rows, two threads per row: eight columns at a time, each thread
+// sums over every other earlier column, the pair combines with one shuffle per column and both
+// finish the 8 x 8 diagonal step.  The block kernel left L^T in the upper triangle of the
+// diagonal block, so the tile loads as it is (coalesced, no transposition) and the inner loop
+// reads eight consecutive entries L[j0..j0+7][i] as two broadcast vector loads.  Plain fp32 FMAs:
+// this is the step that used to need the explicit inverse of the diagonal block on the critical
+// path.
+constexpr int TR = 128;                    // rows per CTA
+constexpr int TRT = 2 * TR;                // threads per CTA
+constexpr int LPITCH = NB + 4, YPITCH = NB + 2;
+constexpr int TRSM_SMEM = (NB * LPITCH + TR * YPITCH + NB) * (int)sizeof(float);
+__global__ void __launch_bounds__(TRT) trsm_panel_kernel(float* __restrict__ A, long long lda, int k0, int rest,
+                                                         long long sW) {
+  A += (long long)blockIdx.y * sW;
+  extern __shared__ __align__(16) float sm[];
+  float* Lt = sm;                           // Lt[i * LPITCH + j] = L[j][i] for j >= i
+  float* Ys = sm + NB * LPITCH;             // this CTA's rows, YPITCH apart
+  float* dinv = Ys + TR * YPITCH;
+  const int tid = threadIdx.x;
+  const float* Lkk = A + (long long)k0 * lda + k0;
+  float* P = A + (long long)(k0 + NB) * lda + k0;
+  const int row0 = blockIdx.x * TR;
+  const int rows = min(TR, rest - row0);
+#pragma unroll
+  for (int it = 0; it < NB * NB / 4 / TRT; ++it) {
+    const int e = it * TRT + tid, i = e / (NB / 4), j4 = e % (NB / 4);
+    const float4 v = *reinterpret_cast<const float4*>(Lkk + (long long)i * lda + 4 * j4);
+    *reinterpret_cast<float4*>(Lt + i * LPITCH + 4 * j4) = v;
+  }
+#pragma unroll
+  for (int it = 0; it < TR * NB / 4 / TRT; ++it) {
+    const int e = it * TRT + tid, r = e / (NB / 4), c4 = e % (NB / 4);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows) v = *reinterpret_cast<const float4*>(P + (long long)(row0 + r) * lda + 4 * c4);
+    float2* dst = reinterpret_cast<float2*>(Ys + r * YPITCH + 4 * c4);
+    dst[0] = make_float2(v.x, v.y);
+    dst[1] = make_float2(v.z, v.w);
+  }
+  __syncthreads();
+  if (tid < NB) dinv[tid] = 1.f / Lt[tid * LPITCH + tid];
+  __syncthreads();
+  {
+    const int r = tid >> 1, half = tid & 1;
+    float* y = Ys + r * YPITCH;
+    for (int j0 = 0; j0 < NB; j0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] = half ? 0.f : y[j0 + c];
+#pragma unroll 4
+      for (int i = half; i < j0; i += 2) {
+        const float yi = y[i];
+        const float4 l0 = *reinterpret_cast<const float4*>(Lt + i * LPITCH + j0);
+        const float4 l1 = *reinterpret_cast<const float4*>(Lt + i * LPITCH + j0 + 4);
+        acc[0] = fmaf(-yi, l0.x, acc[0]); acc[1] = fmaf(-yi, l0.y, acc[1]);
+        acc[2] = fmaf(-yi, l0.z, acc[2]); acc[3] = fmaf(-yi, l0.w, acc[3]);
+        acc[4] = fmaf(-yi, l1.x, acc[4]); acc[5] = fmaf(-yi, l1.y, acc[5]);
+        acc[6] = fmaf(-yi, l1.z, acc[6]); acc[7] = fmaf(-yi, l1.w, acc[7]);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float yc = acc[c] * dinv[j0 + c];
+        acc[c] = yc;
+#pragma unroll
+        for (int c2 = c + 1; c2 < 8; ++c2) acc[c2] = fmaf(-yc, Lt[(j0 + c) * LPITCH + j0 + c2], acc[c2]);
+      }
+      if (half == 0) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) y[j0 + c] = acc[c];
+      }
+      __syncwarp();          // the partner reads these eight values in the next step
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < TR * NB / 4 / TRT; ++it) {
+    const int e = it * TRT + tid, r = e / (NB / 4), c4 = e % (NB / 4);
+    if (r < rows) {
+      const float2* src = reinterpret_cast<const float2*>(Ys + r * YPITCH + 4 * c4);
+      const float2 a = src[0], b = src[1];
+      *reinterpret_cast<float4*>(P + (long long)(row0 + r) * lda + 4 * c4) = make_float4(a.x, a.y, b.x, b.y);
+    }
+  }
+}
+
+// ---- inverses of all diagonal blocks of L, one CTA per block (off the critical path) ----------
+// L block (nb x nb, lower) -> L^-1 written to the matching block of X (lower part; upper part
+// zero).  The 8 x 8 diagonal blocks are inverted at once, then neighbouring inverted blocks are
+// joined level by level (four levels, two small products each).
+constexpr int DINV_SMEM = (2 * NB * (NB + 1) + (NB / 2) * (NB / 2)) * (int)sizeof(float);
+__global__ void __launch_bounds__(256) diag_inverse_kernel(const float* __restrict__ A, long long lda,
+                                                           float* __restrict__ X, long long ldx, int n,
+                                                           long long sW) {
+  A += (long long)blockIdx.y * sW;
+  X += (long long)blockIdx.y * sW;
+  extern __shared__ __align__(16) float sm[];
+  float (*S)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm);                    // L
+  float (*Y)[NB + 1] = reinterpret_cast<float (*)[NB + 1]>(sm + NB * (NB + 1));    // L^-1
+  float* T = sm + 2 * NB * (NB + 1);                                               // [64 * 64]
+  const int tid = threadIdx.x;
+  const int k0 = blockIdx.x * NB, nb = min(NB, n - k0);
+  const float* Ab = A + (long long)k0 * lda + k0;
+  float* Xb = X + (long long)k0 * ldx + k0;
+  for (int e = tid; e < NB * NB; e += 256) {
+    const int r = e / NB, c = e % NB;
+    S[r][c] = (r < nb && c <= r) ? Ab[(long long)r * lda + c] : ((r == c) ? 1.f : 0.f);
+    Y[r][c] = 0.f;
+  }
   __syncthreads();
   if (tid < NB) {
     const int i0 = (tid >> 3) * 8, t = tid & 7;     // column t of the inverse of diagonal block i0
@@ -339,29 +474,27 @@ static int hinv_factor_impl(int batch, const float* H, long long ldh, int n, flo
     OC_CUDA(cudaMemsetAsync(X + b * sW, 0, (size_t)n * ld * sizeof(float), stream));
 
   // ---- blocked right-looking Cholesky --------------------------------------------------
-  const int smem = (2 * NB * (NB + 1) + (NB / 2) * (NB / 2)) * (int)sizeof(float);
-  OC_OPT_IN_SMEM(potrf_diag_kernel, smem);
+  OC_OPT_IN_SMEM(potrf_block_kernel, POTRF_SMEM);
+  OC_OPT_IN_SMEM(trsm_panel_kernel, TRSM_SMEM);
+  OC_OPT_IN_SMEM(diag_inverse_kernel, DINV_SMEM);
   auto batched = [&](OcGemm& g) { g.batch = batch; g.strideA = sW; g.strideB = sW; g.strideC = sW; };
   // Two levels: inside an outer block of OB columns every 128-column panel updates only the
   // rest of that outer block (full height); the matrix behind the outer block is updated once per
   // outer block with K = OB, so it is read and written n/OB times instead of n/128 times.
+  // Per panel the serial chain is: factor the diagonal block (one SM), solve the rows below it
+  // against that block (all SMs, fp32 FMAs), update the rest of the outer block (tensor cores).
   for (int K0 = 0; K0 < n; K0 += OB) {
     const int kend = min(n, K0 + OB);
     for (int k0 = K0; k0 < kend; k0 += NB) {
       const int nb = min(NB, n - k0);
-      potrf_diag_kernel<<<batch, 256, smem, stream>>>(A, ld, X, ld, k0, nb, status, sW);
+      potrf_block_kernel<<<batch, 256, POTRF_SMEM, stream>>>(A, ld, k0, nb, status, sW);
       OC_CHECK_LAUNCH();
       const int rest = n - k0 - nb;
       if (rest <= 0) break;
       float* panel = A + (long long)(k0 + nb) * ld + k0;
-      OcGemm g{};
-      // panel <- panel * (Lkk^-1)^T  (in place: one column tile, every CTA reads its rows first)
-      g.A = panel; g.lda = ld; g.B = X + (long long)k0 * ld + k0; g.ldb = ld; g.C = panel; g.ldc = ld;
-      g.M = rest; g.N = nb; g.K = nb; g.alpha = 1.f; g.beta = 0.f; g.transA = 0; g.transB = 1;
-      g.flags = 0;
-      batched(g);
-      int rc = oc_gemm_f32_launch(g, stream);
-      if (rc) return rc;
+      OC_REQUIRE(nb == NB, "hinv_factor: a panel with rows below it is a full panel");
+      trsm_panel_kernel<<<dim3(oc_div_up(rest, TR), batch), TRT, TRSM_SMEM, stream>>>(A, ld, k0, rest, sW);
+      OC_CHECK_LAUNCH();
       const int inner = kend - (k0 + nb);
       if (inner <= 0) continue;
       // columns [k0+nb, kend) of all rows below the panel's diagonal block (lower tiles only)
@@ -371,7 +504,7 @@ static int hinv_factor_impl(int batch, const float* H, long long ldh, int n, flo
       s.M = rest; s.N = inner; s.K = nb; s.alpha = -1.f; s.beta = 1.f; s.transA = 0; s.transB = 1;
       s.flags = OC_GEMM_SKIP_UPPER_TILES;
       batched(s);
-      rc = oc_gemm_f32_launch(s, stream);
+      int rc = oc_gemm_f32_launch(s, stream);
       if (rc) return rc;
     }
     const int rest2 = n - kend;
@@ -387,6 +520,9 @@ static int hinv_factor_impl(int batch, const float* H, long long ldh, int n, flo
     const int rc2 = oc_gemm_f32_launch(t, stream);
     if (rc2) return rc2;
   }
+  // inverses of the diagonal blocks, all at once: the seeds of the blocked inverse below
+  diag_inverse_kernel<<<dim3(oc_div_up(n, NB), batch), 256, DINV_SMEM, stream>>>(A, ld, X, ld, n, sW);
+  OC_CHECK_LAUNCH();
 
   // ---- recursive blocked inverse of L: X holds the inverted diagonal blocks -----------------
   // One matrix: the uniform problems of a level form one batched product.  Several matrices: the

@@ -731,6 +731,41 @@ class _HostCopier:
 _copier = _HostCopier()
 
 
+class LayerTimer:
+    """Device time of a layer's kernels for ``QuantizationResult.quantization_time`` without stopping
+    the host: events bracket the work on the current stream.  Outside a ``deferred_host_copies``
+    block ``stop`` waits and fills the results at once; inside, the results are filled when the
+    block ends (with the host copies)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        with torch.cuda.device(self.device):
+            self.begin = torch.cuda.Event(enable_timing=True)
+            self.begin.record()
+
+    def stop(self, shares):
+        """``shares``: [(result, fraction of the elapsed time that belongs to it)]."""
+        with torch.cuda.device(self.device):
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+        entry = (self.begin, end, list(shares))
+        if _copier.deferred:
+            _pending_timers.append(entry)
+        else:
+            _resolve_timer(entry)
+
+
+_pending_timers: list = []
+
+
+def _resolve_timer(entry):
+    begin, end, shares = entry
+    end.synchronize()
+    seconds = begin.elapsed_time(end) / 1e3
+    for result, fraction in shares:
+        result.quantization_time = seconds * fraction
+
+
 def to_host(tensors):
     """Copy device tensors to ordinary host tensors (None entries pass through).  Outside a
     ``deferred_host_copies`` block the returned tensors are complete; inside, they are filled in the
@@ -740,6 +775,8 @@ def to_host(tensors):
 
 def finish_host_copies():
     _copier.finish()
+    while _pending_timers:
+        _resolve_timer(_pending_timers.pop(0))
 
 
 class deferred_host_copies:
@@ -753,7 +790,7 @@ class deferred_host_copies:
     def __exit__(self, *exc):
         _copier.deferred = self._previous
         if not _copier.deferred:
-            _copier.finish()
+            finish_host_copies()
         return False
 
 

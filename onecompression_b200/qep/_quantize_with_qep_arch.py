@@ -679,7 +679,7 @@ class BlockQuantizer:
             h, c, n = acc.finalize()
             t0 = self._tick(f"pass_quantized+moments[{gi}]", t0)
             if self.dist is not None:
-                h, c, n = self.dist.reduce_moments(h, c, n)
+                h, c, n = self.dist.reduce_moments(h, c, n, fixed_split=True)
                 t0 = self._tick("allreduce", t0)
             factors = {}
             plan = []            # [(modules sharing one call, factor, excluded)]

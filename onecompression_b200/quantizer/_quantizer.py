@@ -124,14 +124,14 @@ class Quantizer(metaclass=ABCMeta):
         """Forward-hook entry (register_forward_hook signature; reference :219-257)."""
         name = self.module_to_name[module]
         self.logger.debug("Quantizing layer: %s", name)
-        t0 = time.time()
+        timer = self._start_timer(module)
         if hessian is None and self.flag_hessian:
             hessian, nsamples = self.calculate_hessian(module, input)
         extra = {"nsamples": nsamples} if self.flag_nsamples else {}
         result = self.quantize_layer(module, input, hessian=hessian, **extra)
         if isinstance(result, torch.Tensor):
             result = QuantizationResult(dequantized_weight=result)
-        result.quantization_time = self._elapsed(t0, module)
+        self._stop_timer(timer, result)
         self.results[name] = result
         if self.calc_quant_error:
             self._record_quantization_error(module, name, input, result)
@@ -143,7 +143,7 @@ class Quantizer(metaclass=ABCMeta):
         (reference :259-333).  ``factor`` optionally carries a ready inverse-Hessian
         factor of ``hessian`` so that layers sharing one input share one factorisation."""
         name = self.module_to_name[module]
-        t0 = time.time()
+        timer = self._start_timer(module)
         if hessian is None and self.flag_hessian:
             hessian, nsamples = self.calculate_hessian(module, quant_input_activation)
         if delta_hatX is not None or original_input_activation is not None:
@@ -160,16 +160,25 @@ class Quantizer(metaclass=ABCMeta):
         result = self.quantize_layer(module, quant_input_activation, hessian=hessian, **extra)
         if isinstance(result, torch.Tensor):
             result = QuantizationResult(dequantized_weight=result)
-        result.quantization_time = self._elapsed(t0, module)
+        self._stop_timer(timer, result)
         self.results[name] = result
         if self.calc_quant_error:
             self._record_quantization_error(module, name, quant_input_activation, result)
 
     @staticmethod
-    def _elapsed(t0, module):
+    def _start_timer(module):
+        """quantization_time is the device time of the layer's kernels on a CUDA module (events, so
+        that a driver which defers the host copies is not stopped per layer), wall time otherwise."""
         if module.weight.is_cuda:
-            torch.cuda.synchronize(module.weight.device)
-        return time.time() - t0
+            return kernels.LayerTimer(module.weight.device)
+        return time.time()
+
+    @staticmethod
+    def _stop_timer(timer, result):
+        if isinstance(timer, kernels.LayerTimer):
+            timer.stop([(result, 1.0)])
+        else:
+            result.quantization_time = time.time() - timer
 
     def _record_quantization_error(self, module, name, input, result):  # pylint: disable=redefined-builtin
         deq = result.compute_dequantized_weight()

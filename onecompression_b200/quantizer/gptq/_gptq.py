@@ -321,10 +321,8 @@ class GPTQ(Quantizer):
         """``quantize_with_qep`` for several layers that share ``hessian`` (equal ``stack_key``):
         one correction and one column loop over the row-wise concatenation of their weights.
         Returns {module: GPTQResult}; results are identical to the per-layer calls."""
-        import time
-
-        t0 = time.time()
         first = modules[0]
+        timer = kernels.LayerTimer(first.weight.device)
         name0 = self.module_to_name[first]
         bits = GPTQ.resolve_bits(name0, self.wbits, self.mlp_wbits, self.module_wbits)
         gs = GPTQ.resolve_groupsize(name0, self.groupsize, self.mlp_groupsize)
@@ -356,8 +354,6 @@ class GPTQ(Quantizer):
             pieces.append(out["scales"][:, r0:r0 + r])
             r0 += r
         host = kernels.to_host(pieces + [perm] * len(rows))     # may still be in flight: do not read here
-        torch.cuda.synchronize(stacked.device)
-        elapsed = time.time() - t0
         results, r0 = {}, 0
         for i, (m, r) in enumerate(zip(modules, rows)):
             qweight, qzeros, scales = host[3 * i], host[3 * i + 1], host[3 * i + 2]
@@ -371,9 +367,11 @@ class GPTQ(Quantizer):
                 qweight_is_packed=packed, qzeros_is_packed=packed, qweight_original_shape=(r, d),
             )
             res.__dict__["_device_dequantized"] = out["dequantized"][r0:r0 + r]
-            res.quantization_time = elapsed * r / sum(rows)
             results[m] = res
             r0 += r
+        # device time of the stacked call, shared out by rows (filled with the host copies when the
+        # caller defers those)
+        timer.stop([(results[m], r / sum(rows)) for m, r in zip(modules, rows)])
         return results
 
     # ------------------------------------------------------------------ many small layers, own Hessians

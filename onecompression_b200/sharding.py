@@ -46,13 +46,22 @@ class ShardedContext:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self._totals = {}
 
     # ---- tokens -------------------------------------------------------------------
-    def reduce_moments(self, h: torch.Tensor, c: Optional[torch.Tensor], n: int):
-        """Per-rank means (2/n_r)·Σ_r → global means (2/N)·Σ.  Returns (h, c, N)."""
-        total = torch.tensor([float(n)], dtype=torch.float64, device=h.device)
-        dist.all_reduce(total, group=self.group)
-        big_n = int(total.item())
+    def reduce_moments(self, h: torch.Tensor, c: Optional[torch.Tensor], n: int, fixed_split: bool = False):
+        """Per-rank means (2/n_r)·Σ_r → global means (2/N)·Σ.  Returns (h, c, N).
+
+        ``fixed_split``: the caller's token split over the ranks does not change between calls with
+        the same local count (the calibration sequences of a run), so the global count is
+        exchanged once and remembered, which saves a host synchronisation per call."""
+        big_n = self._totals.get(n) if fixed_split else None
+        if big_n is None:
+            total = torch.tensor([float(n)], dtype=torch.float64, device=h.device)
+            dist.all_reduce(total, group=self.group)
+            big_n = int(total.item())
+            if fixed_split:
+                self._totals[n] = big_n
         w = (n / big_n) if big_n > 0 else 0.0
         h.mul_(w)
         dist.all_reduce(h, group=self.group)
@@ -103,7 +112,8 @@ class ShardedContext:
         from .quantizer.gptq._gptq import GPTQ, GPTQResult
 
         names = [quantizer.module_to_name[m] for m in modules]
-        t0 = time.time()
+        on_gpu = modules[0].weight.is_cuda
+        timer = kernels.LayerTimer(modules[0].weight.device) if on_gpu else time.time()
         bits = GPTQ.resolve_bits(names[0], quantizer.wbits, quantizer.mlp_wbits, quantizer.module_wbits)
         gs = GPTQ.resolve_groupsize(names[0], quantizer.groupsize, quantizer.mlp_groupsize)
         rows = [m.weight.shape[0] for m in modules]
@@ -181,9 +191,6 @@ class ShardedContext:
         else:
             host = [p.contiguous() for p in pieces] + [perm64.clone() if perm64 is not None else None
                                                        for _ in rows]
-        if weight.is_cuda:
-            torch.cuda.synchronize(weight.device)
-        elapsed = time.time() - t0
         results, r0 = {}, 0
         for i, (m, name, r) in enumerate(zip(modules, names, rows)):
             qw, sc, qz = host[3 * i], host[3 * i + 1], host[3 * i + 2]
@@ -196,10 +203,14 @@ class ShardedContext:
                 qweight_is_packed=packed, qzeros_is_packed=packed, qweight_original_shape=(r, d),
             )
             result.__dict__["_device_dequantized"] = w_hat[r0:r0 + r]
-            result.quantization_time = elapsed * r / out_features
             quantizer.results[name] = result
             results[m] = result
             r0 += r
+        if on_gpu:
+            timer.stop([(results[m], r / out_features) for m, r in zip(modules, rows)])
+        else:
+            for m, r in zip(modules, rows):
+                results[m].quantization_time = (time.time() - timer) * r / out_features
         return results
 
     # ---- independent layers (MoE experts) ---------------------------------------------
