@@ -122,9 +122,10 @@ __global__ void reverse_upper_kernel(const float* __restrict__ X, long long ldx,
 // and continues with pivot 1 so that every later kernel still terminates.
 //
 // 16 x 16 threads, each holding an 8 x 8 sub-block in registers.  The eight columns of a
-// micro-panel are finished inside the one warp that holds that block column (shuffles only),
-// published to shared memory, and every thread to the right applies them as eight rank-1 updates
-// to its registers: one barrier per eight columns.
+// micro-panel are finished inside the one warp that holds that block column (the diagonal 8 x 8
+// block on one lane, its factor shuffled to the others), published to shared memory, and every
+// thread to the right applies them as eight rank-1 updates to its registers: one barrier per
+// eight columns.
 constexpr int POTRF_SMEM = (NB * (NB + 4) + 2 * 8 * (NB + 4)) * (int)sizeof(float);
 __global__ void __launch_bounds__(256) potrf_block_kernel(float* __restrict__ A, long long lda, int k0, int nb,
                                                           int* __restrict__ status, long long sW) {
@@ -172,40 +173,66 @@ __global__ void __launch_bounds__(256) potrf_block_kernel(float* __restrict__ A,
   for (int jb = 0; jb < NB / 8; ++jb) {
     const int buf = jb & 1;
     if ((tid >> 5) == (jb >> 1)) {
-      // ---- the micro-panel's eight columns inside one warp (shuffles, no barrier) ----
+      // ---- the micro-panel's eight columns, inside the one warp that holds them ----
+      // The lane with the diagonal 8 x 8 block factors it alone in registers; the factor's 28
+      // sub-diagonal entries and 8 reciprocal pivots go round by shuffles, and every other lane of
+      // the block column solves X L^T = B for its own 8 x 8 block by forward substitution: eight
+      // independent rows per lane, the same operations in the same order as a column-by-column
+      // elimination across the lanes, without its eight broadcast-scale-update rounds.
       const int pl = ((jb & 1) << 4) + jb;          // lane that owns the diagonal 8 x 8 block
-      const bool mine = (tx == jb) && (ty >= jb);
+      const bool mine = (tx == jb) && (ty > jb);
       const bool is_pivot = (tx == jb) && (ty == jb);
+      float l[8][8], dinv[8];
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) {
-        float p = __shfl_sync(0xffffffffu, a[jj][jj], pl);
-        if (!(p > 0.f) || !isfinite(p)) {
-          if (is_pivot) atomicCAS(status, 0, k0 + jb * 8 + jj + 1);
-          p = 1.f;
-        }
-        // the only serial arithmetic of a column step: one approximate reciprocal square root,
-        // refined once, instead of an IEEE square root followed by an IEEE division
-        float inv = rsqrtf(p);
-        inv = inv * fmaf(-0.5f * p * inv, inv, 1.5f);
-        const float piv = p * inv;
-        if (is_pivot) a[jj][jj] = piv;
-        if (mine) {
+      for (int i = 0; i < 8; ++i) {
+        dinv[i] = 0.f;
 #pragma unroll
-          for (int ii = 0; ii < 8; ++ii)
-            if (!is_pivot || ii > jj) a[ii][jj] *= inv;
-        }
+        for (int j = 0; j < 8; ++j) l[i][j] = 0.f;
+      }
+      if (is_pivot) {
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          if (cc <= jj) continue;
-          const float lc = __shfl_sync(0xffffffffu, a[cc][jj], pl);   // L[8 jb + cc][8 jb + jj]
-          if (mine) {
-#pragma unroll
-            for (int ii = 0; ii < 8; ++ii)
-              if (!is_pivot || ii >= cc) a[ii][cc] = fmaf(-a[ii][jj], lc, a[ii][cc]);
+        for (int jj = 0; jj < 8; ++jj) {
+          float p = a[jj][jj];
+          if (!(p > 0.f) || !isfinite(p)) {
+            atomicCAS(status, 0, k0 + jb * 8 + jj + 1);
+            p = 1.f;
           }
+          // one approximate reciprocal square root, refined once, instead of an IEEE square
+          // root followed by IEEE divisions
+          float inv = rsqrtf(p);
+          inv = inv * fmaf(-0.5f * p * inv, inv, 1.5f);
+          dinv[jj] = inv;
+          a[jj][jj] = p * inv;
+#pragma unroll
+          for (int ii = jj + 1; ii < 8; ++ii) a[ii][jj] *= inv;
+#pragma unroll
+          for (int cc = jj + 1; cc < 8; ++cc)
+#pragma unroll
+            for (int ii = cc; ii < 8; ++ii) a[ii][cc] = fmaf(-a[ii][jj], a[cc][jj], a[ii][cc]);
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < i; ++j) l[i][j] = a[i][j];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dinv[i] = __shfl_sync(0xffffffffu, dinv[i], pl);
+#pragma unroll
+        for (int j = 0; j < i; ++j) l[i][j] = __shfl_sync(0xffffffffu, l[i][j], pl);
       }
       if (mine) {
+#pragma unroll
+        for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float acc = a[ii][j];
+#pragma unroll
+            for (int k = 0; k < j; ++k) acc = fmaf(-a[ii][k], l[j][k], acc);
+            a[ii][j] = acc * dinv[j];
+          }
+      }
+      if (mine || is_pivot) {
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj)
 #pragma unroll
@@ -224,11 +251,11 @@ __global__ void __launch_bounds__(256) potrf_block_kernel(float* __restrict__ A,
         const float4 c_hi = *reinterpret_cast<const float4*>(&Lp[buf][jj][c0 + 4]);
         const float rc[8] = {r_lo.x, r_lo.y, r_lo.z, r_lo.w, r_hi.x, r_hi.y, r_hi.z, r_hi.w};
         const float cv[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+        // (the entries above the diagonal of a diagonal block are updated too: nothing reads them)
 #pragma unroll
         for (int ii = 0; ii < 8; ++ii)
 #pragma unroll
-          for (int cc = 0; cc < 8; ++cc)
-            if (ty > tx || ii >= cc) a[ii][cc] = fmaf(-rc[ii], cv[cc], a[ii][cc]);
+          for (int cc = 0; cc < 8; ++cc) a[ii][cc] = fmaf(-rc[ii], cv[cc], a[ii][cc]);
       }
     }
   }
@@ -265,8 +292,10 @@ __global__ void __launch_bounds__(256) potrf_block_kernel(float* __restrict__ A,
 // this is the step that used to need the explicit inverse of the diagonal block on the critical
 // path.
 constexpr int TR = 128;                    // rows per CTA
-constexpr int TRT = 2 * TR;                // threads per CTA
-constexpr int LPITCH = NB + 4, YPITCH = NB + 2;
+constexpr int TPR = 2;                     // threads per row (four were measured slower: the 8 x 8
+                                           // diagonal step is repeated by every thread of a row)
+constexpr int TRT = TPR * TR;              // threads per CTA
+constexpr int LPITCH = NB + 4, YPITCH = NB + 2;   // YPITCH = 2 mod 32: a warp's rows hit distinct banks
 constexpr int TRSM_SMEM = (NB * LPITCH + TR * YPITCH + NB) * (int)sizeof(float);
 __global__ void __launch_bounds__(TRT) trsm_panel_kernel(float* __restrict__ A, long long lda, int k0, int rest,
                                                          long long sW) {
@@ -299,14 +328,14 @@ __global__ void __launch_bounds__(TRT) trsm_panel_kernel(float* __restrict__ A, 
   if (tid < NB) dinv[tid] = 1.f / Lt[tid * LPITCH + tid];
   __syncthreads();
   {
-    const int r = tid >> 1, half = tid & 1;
+    const int r = tid / TPR, part = tid % TPR;
     float* y = Ys + r * YPITCH;
     for (int j0 = 0; j0 < NB; j0 += 8) {
       float acc[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) acc[c] = half ? 0.f : y[j0 + c];
+      for (int c = 0; c < 8; ++c) acc[c] = part ? 0.f : y[j0 + c];
 #pragma unroll 4
-      for (int i = half; i < j0; i += 2) {
+      for (int i = part; i < j0; i += TPR) {
         const float yi = y[i];
         const float4 l0 = *reinterpret_cast<const float4*>(Lt + i * LPITCH + j0);
         const float4 l1 = *reinterpret_cast<const float4*>(Lt + i * LPITCH + j0 + 4);
@@ -316,19 +345,27 @@ __global__ void __launch_bounds__(TRT) trsm_panel_kernel(float* __restrict__ A, 
         acc[6] = fmaf(-yi, l1.z, acc[6]); acc[7] = fmaf(-yi, l1.w, acc[7]);
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+      for (int c = 0; c < 8; ++c) {
+        acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 1);
+        if (TPR == 4) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], 2);
+      }
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const float yc = acc[c] * dinv[j0 + c];
         acc[c] = yc;
+        if (c < 7) {
+          const float4 l0 = *reinterpret_cast<const float4*>(Lt + (j0 + c) * LPITCH + j0);
+          const float4 l1 = *reinterpret_cast<const float4*>(Lt + (j0 + c) * LPITCH + j0 + 4);
+          const float lr[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
 #pragma unroll
-        for (int c2 = c + 1; c2 < 8; ++c2) acc[c2] = fmaf(-yc, Lt[(j0 + c) * LPITCH + j0 + c2], acc[c2]);
+          for (int c2 = c + 1; c2 < 8; ++c2) acc[c2] = fmaf(-yc, lr[c2], acc[c2]);
+        }
       }
-      if (half == 0) {
+      if (part == 0) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) y[j0 + c] = acc[c];
       }
-      __syncwarp();          // the partner reads these eight values in the next step
+      __syncwarp();          // the partners read these eight values in the next step
     }
   }
   __syncthreads();

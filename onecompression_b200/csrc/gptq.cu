@@ -91,9 +91,25 @@ __device__ __noinline__ void fit_group(const float* __restrict__ src, int n, int
   *scale = s; *zero = z;
 }
 
-// WARPS*32 rows per CTA; the CTA always has LOADERS threads so that filling the two shared
-// tiles is not left to a single warp when a CTA owns few rows.
+// WARPS*32 rows per CTA; the CTA always has LOADERS threads.  The threads beyond the rows load the
+// tiles, and when a CTA owns few rows (WARPS <= 2) they also take over the deferred updates: after
+// each window of SUB columns the row owners publish the window's errors, the helper threads first
+// bring the next window's columns up to date (the owners wait for that), then the rest of the block
+// while the owners already work on the next window.  Every element still receives its updates in
+// ascending order of the source column with the same two roundings each, so results do not depend
+// on who applies them.
 constexpr int LOADERS = 256;
+
+__device__ __forceinline__ void apply_window(float4& t, const float* __restrict__ es, const float* __restrict__ us) {
+  // es: this row's SUB errors (stride = rows of the CTA is folded in by the caller); us: U rows of the window
+#pragma unroll
+  for (int i = 0; i < SUB; ++i) {
+    const float e = es[i];
+    const float4 u = *reinterpret_cast<const float4*>(us + i * BLK);
+    t.x = __fsub_rn(t.x, __fmul_rn(e, u.x)); t.y = __fsub_rn(t.y, __fmul_rn(e, u.y));
+    t.z = __fsub_rn(t.z, __fmul_rn(e, u.z)); t.w = __fsub_rn(t.w, __fmul_rn(e, u.w));
+  }
+}
 
 // ALIGNED: every group starts on a multiple of SUB columns (per-channel, or a group size that is
 // a multiple of SUB), so the fit can only fall on the first column of a register window and the
@@ -101,9 +117,11 @@ constexpr int LOADERS = 256;
 template <int WARPS, bool ALIGNED>
 __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
   extern __shared__ __align__(16) float sm[];
-  float* Us = sm;               // [BLK][BLK], upper triangle of the diagonal block of U
-  float* Ws = sm + BLK * BLK;   // [WARPS*32][WS], block-entry values of the rows' columns
   constexpr int NROWS = WARPS * 32;
+  constexpr bool HELPERS = WARPS <= 2;
+  float* Us = sm;               // [BLK][BLK], upper triangle of the diagonal block of U
+  float* Ws = sm + BLK * BLK;   // [NROWS][WS], block-entry values of the rows' columns
+  float* Es = Ws + NROWS * WS;  // [2][SUB][NROWS] errors of the last two windows (helpers only)
   const int tid = threadIdx.x;
   const int row0 = blockIdx.x * NROWS;
   const int count = a.count, i1 = a.i1;
@@ -113,90 +131,155 @@ __global__ void __launch_bounds__(LOADERS) gptq_block_kernel(ColArgs a) {
     a.scales += b * a.sS; a.zeros += b * a.sS;
   }
 
-  for (int e = tid; e < BLK * BLK; e += LOADERS) {
-    const int i = e / BLK, j = e % BLK;
-    Us[e] = (i < count && j < count && j >= i) ? a.U[(long long)(i1 + i) * a.ldu + i1 + j] : 0.f;
-  }
-  for (int e = tid; e < NROWS * BLK; e += LOADERS) {
-    const int r = e / BLK, c = e % BLK;
-    Ws[r * WS + c] = (row0 + r < a.out && c < count) ? a.Wf[(long long)(row0 + r) * a.ldw + i1 + c] : 0.f;
+  // whole block, 16-byte aligned rows: vector loads (the part of U below the diagonal is never used)
+  const bool vec = count == BLK && (i1 & 3) == 0 && (a.ldu & 3) == 0 && (a.ldw & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a.U) | reinterpret_cast<uintptr_t>(a.Wf)) & 15) == 0;
+  if (vec) {
+#pragma unroll
+    for (int it = 0; it < BLK * BLK / 4 / LOADERS; ++it) {
+      const int e = it * LOADERS + tid, i = e / (BLK / 4), j4 = e % (BLK / 4);
+      *reinterpret_cast<float4*>(Us + i * BLK + 4 * j4) =
+          *reinterpret_cast<const float4*>(a.U + (long long)(i1 + i) * a.ldu + i1 + 4 * j4);
+    }
+#pragma unroll
+    for (int it = 0; it < NROWS * BLK / 4 / LOADERS; ++it) {
+      const int e = it * LOADERS + tid, r = e / (BLK / 4), c4 = e % (BLK / 4);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row0 + r < a.out) v = *reinterpret_cast<const float4*>(a.Wf + (long long)(row0 + r) * a.ldw + i1 + 4 * c4);
+      *reinterpret_cast<float4*>(Ws + r * WS + 4 * c4) = v;
+    }
+  } else {
+    for (int e = tid; e < BLK * BLK; e += LOADERS) {
+      const int i = e / BLK, j = e % BLK;
+      Us[e] = (i < count && j < count && j >= i) ? a.U[(long long)(i1 + i) * a.ldu + i1 + j] : 0.f;
+    }
+    for (int e = tid; e < NROWS * BLK; e += LOADERS) {
+      const int r = e / BLK, c = e % BLK;
+      Ws[r * WS + c] = (row0 + r < a.out && c < count) ? a.Wf[(long long)(row0 + r) * a.ldw + i1 + c] : 0.f;
+    }
   }
   __syncthreads();
 
   const int row = row0 + tid;
-  if (tid >= NROWS || row >= a.out) return;
-  float* wrow = Ws + tid * WS;
-  const float* grow = a.Wf + (long long)row * a.ldw;  // block-entry state of the whole row
+  const bool owner = tid < NROWS && row < a.out;
+  // helpers take the deferred updates when the block's columns come in whole groups of four
+  const bool helped = HELPERS && (count & 3) == 0;
+  if (!helped && !owner) return;
+  float* wrow = Ws + (owner ? tid : 0) * WS;
+  const float* grow = a.Wf + (long long)(owner ? row : 0) * a.ldw;  // block-entry state of the whole row
   const float maxqf = (float)a.maxq;
   const int gs = a.gs;
   unsigned short* code_out = a.codesT + (long long)i1 * a.out + row;   // + column * out
   float* err_out = a.ErrT + row;                                        // + column * lde
-  float scale, zero;
-  if (gs == -1) { scale = a.scales[row]; zero = a.zeros[row]; }
-  else if (i1 % gs != 0) {
-    // the block starts inside a group opened by an earlier block: continue with its parameters
-    scale = a.scales[(long long)(i1 / gs) * a.out + row];
-    zero = a.zeros[(long long)(i1 / gs) * a.out + row];
-  } else { scale = 1.f; zero = 0.f; }
+  float scale = 1.f, zero = 0.f;
+  if (owner) {
+    if (gs == -1) { scale = a.scales[row]; zero = a.zeros[row]; }
+    else if (i1 % gs != 0) {
+      // the block starts inside a group opened by an earlier block: continue with its parameters
+      scale = a.scales[(long long)(i1 / gs) * a.out + row];
+      zero = a.zeros[(long long)(i1 / gs) * a.out + row];
+    }
+  }
+  // helper thread -> (row, every nsel-th group of four columns)
+  constexpr int NSEL = HELPERS ? (LOADERS - NROWS) / NROWS : 1;
+  const int hrow = (tid - NROWS) % NROWS, gsel = (tid - NROWS) / NROWS;
+  const bool helper = helped && tid >= NROWS && gsel < NSEL;
 
   for (int cb = 0; cb < count; cb += SUB) {
-    float w[SUB], er[SUB];
+    float* es_buf = Es + ((cb / SUB) & 1) * SUB * NROWS;
+    if (owner) {
+      float w[SUB], er[SUB];
 #pragma unroll
-    for (int v = 0; v < SUB / 4; ++v) {
-      const float4 t = *reinterpret_cast<const float4*>(wrow + cb + 4 * v);
-      w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
-    }
-#pragma unroll
-    for (int i = 0; i < SUB; ++i) {
-      const int ci = cb + i;
-      er[i] = 0.f;
-      if (ci < count) {
-        const int col = i1 + ci;
-        if ((!ALIGNED || i == 0) && gs != -1 && col % gs == 0) {
-          const int n = min(gs, a.d - col);
-          // the shared tile is still pristine only at the very first column of the block
-          fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, a.mse_steps,
-                    a.mse_grid, a.mse_norm, &scale, &zero);
-          const int g = col / gs;
-          a.scales[(long long)g * a.out + row] = scale;
-          a.zeros[(long long)g * a.out + row] = zero;
-        }
-        const float x = w[i];
-        float q = __fadd_rn(rintf(__fdiv_rn(x, scale)), zero);
-        q = fminf(fmaxf(q, 0.f), maxqf);
-        const float dq = __fmul_rn(scale, __fsub_rn(q, zero));
-        const float e = __fdiv_rn(__fsub_rn(x, dq), Us[ci * BLK + ci]);
-        er[i] = e;
-        code_out[(long long)ci * a.out] = (unsigned short)q;
-        err_out[(long long)ci * a.lde] = e;
-        const float4* up = reinterpret_cast<const float4*>(Us + ci * BLK + cb);
-#pragma unroll
-        for (int j4 = (i + 1) / 4; j4 < SUB / 4; ++j4) {
-          const float4 u = up[j4];
-          if (4 * j4 + 0 > i) w[4 * j4 + 0] = __fsub_rn(w[4 * j4 + 0], __fmul_rn(e, u.x));
-          if (4 * j4 + 1 > i) w[4 * j4 + 1] = __fsub_rn(w[4 * j4 + 1], __fmul_rn(e, u.y));
-          if (4 * j4 + 2 > i) w[4 * j4 + 2] = __fsub_rn(w[4 * j4 + 2], __fmul_rn(e, u.z));
-          if (4 * j4 + 3 > i) w[4 * j4 + 3] = __fsub_rn(w[4 * j4 + 3], __fmul_rn(e, u.w));
-        }
+      for (int v = 0; v < SUB / 4; ++v) {
+        const float4 t = *reinterpret_cast<const float4*>(wrow + cb + 4 * v);
+        w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
       }
-    }
-    // Later columns of the block receive this sub-block's 32 updates now, in the
-    // same order (ascending source column) and with the same two roundings each.
-    for (int jc = cb + SUB; jc < count; jc += 8) {
-      float4 t0 = *reinterpret_cast<const float4*>(wrow + jc);
-      float4 t1 = *reinterpret_cast<const float4*>(wrow + jc + 4);
 #pragma unroll
       for (int i = 0; i < SUB; ++i) {
-        const float e = er[i];
-        const float4 u0 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc);
-        const float4 u1 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc + 4);
-        t0.x = __fsub_rn(t0.x, __fmul_rn(e, u0.x)); t0.y = __fsub_rn(t0.y, __fmul_rn(e, u0.y));
-        t0.z = __fsub_rn(t0.z, __fmul_rn(e, u0.z)); t0.w = __fsub_rn(t0.w, __fmul_rn(e, u0.w));
-        t1.x = __fsub_rn(t1.x, __fmul_rn(e, u1.x)); t1.y = __fsub_rn(t1.y, __fmul_rn(e, u1.y));
-        t1.z = __fsub_rn(t1.z, __fmul_rn(e, u1.z)); t1.w = __fsub_rn(t1.w, __fmul_rn(e, u1.w));
+        const int ci = cb + i;
+        er[i] = 0.f;
+        if (ci < count) {
+          const int col = i1 + ci;
+          if ((!ALIGNED || i == 0) && gs != -1 && col % gs == 0) {
+            const int n = min(gs, a.d - col);
+            // the shared tile is still pristine only at the very first column of the block
+            fit_group((ci == 0 && n <= count) ? wrow : grow + col, n, a.maxq, a.sym, a.mse_steps,
+                      a.mse_grid, a.mse_norm, &scale, &zero);
+            const int g = col / gs;
+            a.scales[(long long)g * a.out + row] = scale;
+            a.zeros[(long long)g * a.out + row] = zero;
+          }
+          const float x = w[i];
+          float q = __fadd_rn(rintf(__fdiv_rn(x, scale)), zero);
+          q = fminf(fmaxf(q, 0.f), maxqf);
+          const float dq = __fmul_rn(scale, __fsub_rn(q, zero));
+          const float e = __fdiv_rn(__fsub_rn(x, dq), Us[ci * BLK + ci]);
+          er[i] = e;
+          code_out[(long long)ci * a.out] = (unsigned short)q;
+          err_out[(long long)ci * a.lde] = e;
+          const float4* up = reinterpret_cast<const float4*>(Us + ci * BLK + cb);
+#pragma unroll
+          for (int j4 = (i + 1) / 4; j4 < SUB / 4; ++j4) {
+            const float4 u = up[j4];
+            if (4 * j4 + 0 > i) w[4 * j4 + 0] = __fsub_rn(w[4 * j4 + 0], __fmul_rn(e, u.x));
+            if (4 * j4 + 1 > i) w[4 * j4 + 1] = __fsub_rn(w[4 * j4 + 1], __fmul_rn(e, u.y));
+            if (4 * j4 + 2 > i) w[4 * j4 + 2] = __fsub_rn(w[4 * j4 + 2], __fmul_rn(e, u.z));
+            if (4 * j4 + 3 > i) w[4 * j4 + 3] = __fsub_rn(w[4 * j4 + 3], __fmul_rn(e, u.w));
+          }
+        }
       }
-      *reinterpret_cast<float4*>(wrow + jc) = t0;
-      *reinterpret_cast<float4*>(wrow + jc + 4) = t1;
+      if (helped) {
+#pragma unroll
+        for (int i = 0; i < SUB; ++i) es_buf[i * NROWS + tid] = er[i];
+      } else {
+        // Later columns of the block receive this sub-block's updates now, in the
+        // same order (ascending source column) and with the same two roundings each.
+        for (int jc = cb + SUB; jc < count; jc += 8) {
+          float4 t0 = *reinterpret_cast<const float4*>(wrow + jc);
+          float4 t1 = *reinterpret_cast<const float4*>(wrow + jc + 4);
+#pragma unroll
+          for (int i = 0; i < SUB; ++i) {
+            const float e = er[i];
+            const float4 u0 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc);
+            const float4 u1 = *reinterpret_cast<const float4*>(Us + (cb + i) * BLK + jc + 4);
+            t0.x = __fsub_rn(t0.x, __fmul_rn(e, u0.x)); t0.y = __fsub_rn(t0.y, __fmul_rn(e, u0.y));
+            t0.z = __fsub_rn(t0.z, __fmul_rn(e, u0.z)); t0.w = __fsub_rn(t0.w, __fmul_rn(e, u0.w));
+            t1.x = __fsub_rn(t1.x, __fmul_rn(e, u1.x)); t1.y = __fsub_rn(t1.y, __fmul_rn(e, u1.y));
+            t1.z = __fsub_rn(t1.z, __fmul_rn(e, u1.z)); t1.w = __fsub_rn(t1.w, __fmul_rn(e, u1.w));
+          }
+          *reinterpret_cast<float4*>(wrow + jc) = t0;
+          *reinterpret_cast<float4*>(wrow + jc + 4) = t1;
+        }
+      }
+    }
+    if (helped) {
+      if (cb + SUB >= count) break;         // the last window has nothing to its right
+      __syncthreads();                      // the window's errors are published
+      const int g_first = (cb + SUB) / 4, g_urgent = min(count, cb + 2 * SUB) / 4, g_end = count / 4;
+      if (helper) {
+        // the next window's columns first: the row owners wait for these
+        for (int g = g_first; g < g_urgent; ++g) {
+          if (g % NSEL != gsel) continue;
+          float4 t = *reinterpret_cast<const float4*>(Ws + hrow * WS + 4 * g);
+          float er[SUB];
+#pragma unroll
+          for (int i = 0; i < SUB; ++i) er[i] = es_buf[i * NROWS + hrow];
+          apply_window(t, er, Us + cb * BLK + 4 * g);
+          *reinterpret_cast<float4*>(Ws + hrow * WS + 4 * g) = t;
+        }
+      }
+      __syncthreads();                      // the next window may start
+      if (helper) {
+        float er[SUB];
+#pragma unroll
+        for (int i = 0; i < SUB; ++i) er[i] = es_buf[i * NROWS + hrow];
+        for (int g = g_urgent; g < g_end; ++g) {
+          if (g % NSEL != gsel) continue;
+          float4 t = *reinterpret_cast<const float4*>(Ws + hrow * WS + 4 * g);
+          apply_window(t, er, Us + cb * BLK + 4 * g);
+          *reinterpret_cast<float4*>(Ws + hrow * WS + 4 * g) = t;
+        }
+      }
     }
   }
 }
@@ -390,7 +473,8 @@ __global__ void unpermute_outputs_kernel(const unsigned short* __restrict__ code
 
 template <int WARPS, bool ALIGNED>
 int launch_block_t(const ColArgs& a, cudaStream_t stream) {
-  const int smem = (BLK * BLK + WARPS * 32 * WS) * (int)sizeof(float);
+  // tiles, plus the error windows the helper threads read (only CTAs with few rows have helpers)
+  const int smem = (BLK * BLK + WARPS * 32 * WS + (WARPS <= 2 ? 2 * SUB * WARPS * 32 : 0)) * (int)sizeof(float);
   OC_OPT_IN_SMEM((gptq_block_kernel<WARPS, ALIGNED>), smem);
   gptq_block_kernel<WARPS, ALIGNED><<<dim3(oc_div_up(a.out, WARPS * 32), a.batch), LOADERS, smem, stream>>>(a);
   OC_CHECK_LAUNCH();
