@@ -277,8 +277,57 @@ def main(ref_root):
              rtn_deq=_np(r["dequantized_weight"]))
     b["rtn_deq_is_bf16"] = np.int64(r["dequantized_weight"].dtype == torch.bfloat16)
     np.savez_compressed(os.path.join(HERE, "bf16.npz"), **b)
+    layer_state_fixture(ref_gptq, ref_layer)
     driver_fixtures(ref_gptq, ref_arch)
     print("golden fixtures written to", HERE)
+
+
+def layer_state_fixture(ref_gptq, ref_layer):
+    """What the save path writes per layer and into config.json: the buffers of the reference's
+    GPTQLinear built from a result (onecomp/quantizer/gptq/gptq_layer.py:395-433, 576-628) for four of
+    the GPTQ cases above, and the quantization_config of plain and mixed-precision quantizers
+    (onecomp/quantizer/gptq/_gptq.py:480-566)."""
+    import json
+
+    out = {}
+    wanted = ("b4_g128_asym", "b4_g128_asym_actorder", "b3_g128_sym", "b8_perchannel_sym")
+    for k, (name, rows, d, ntok, kw) in enumerate(GPTQ_CASES):
+        if name not in wanted:
+            continue
+        kw = dict(kw)
+        kw.pop("_dead", None)
+        w, x = synth_layer(100 + k, rows, d, ntok)
+        lin = torch.nn.Linear(d, rows, bias=True).half()
+        lin.weight.data = w.clone()
+        g = torch.Generator().manual_seed(900 + k)
+        lin.bias.data = (torch.randn(rows, generator=g) * 0.1).half()
+        qz = ref_gptq.GPTQ(**kw)
+        qz.module_to_name = {lin: "layer"}
+        h, _n = qz.calculate_hessian(lin, x.unsqueeze(0))
+        res = qz.quantize_layer(lin, None, hessian=h.clone())
+        layer = ref_layer.GPTQLinear.from_quantization_result(res, bias=lin.bias.data, device="cpu",
+                                                              pack_weights=True, use_gemlite=False)
+        state = layer.state_dict()
+        out[f"{name}/keys"] = np.array(list(state))
+        for key, t in state.items():
+            out[f"{name}/{key}"] = _np(t)
+            out[f"{name}/{key}/dtype"] = np.array(str(t.dtype))
+    names = [f"model.layers.{i}.{n}" for i in range(2) for n in
+             ("self_attn.q_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.down_proj")] + ["lm_head"]
+    configs = {
+        "plain": dict(wbits=4, groupsize=128, sym=False, actorder=True),
+        "mixed": dict(wbits=4, groupsize=128, mlp_wbits=3, mlp_groupsize=64,
+                      module_wbits={"model.layers.1.self_attn.q_proj": 2}),
+    }
+    for tag, kw in configs.items():
+        qz = ref_gptq.GPTQ(**kw)
+        cfg = qz.get_quant_config()
+        out[f"config/{tag}/kwargs"] = np.array(json.dumps(kw))
+        out[f"config/{tag}/quant_config"] = np.array(json.dumps(cfg, sort_keys=True))
+        final = qz.finalize_quant_config_for_save(dict(cfg), names, num_hidden_layers=2)
+        out[f"config/{tag}/final"] = np.array(json.dumps(final, sort_keys=True))
+    out["config/names"] = np.array(names)
+    np.savez_compressed(os.path.join(HERE, "layer_state.npz"), **out)
 
 
 class _FakeModelConfig:
@@ -346,6 +395,56 @@ def _run_reference_driver(ref_gptq, ref_arch, model, ids, quantizer_kw, tag, ext
     np.savez_compressed(os.path.join(HERE, f"driver_{tag}.npz"), **out)
 
 
+def _run_reference_generic_driver(ref_gptq, model, ids, quantizer_kw, tag, extra):
+    """The reference's generic driver run_quantize_with_qep (onecomp/qep/_quantize_with_qep.py:35-133)
+    on CPU: one forward per layer, every layer computes its own H (calculate_hessian) and C
+    (calculate_delta_hatX) from captured activations.  Records both per layer, the order, and the
+    results."""
+    from onecomp.qep import _quantize_with_qep as ref_generic
+    from onecomp.qep._qep_config import QEPConfig
+
+    original = ref_generic.prepare_calibration_dataset
+    ref_generic.prepare_calibration_dataset = lambda **_kw: {"input_ids": ids}
+    order, hs, cs = [], {}, {}
+
+    class Recording(ref_gptq.GPTQ):
+        def calculate_hessian(self, module, input):  # pylint: disable=redefined-builtin
+            h, n = super().calculate_hessian(module, input)
+            name = self.module_to_name[module]
+            if name not in hs:
+                order.append(name)
+                hs[name] = h.clone()
+            return h, n
+
+        def calculate_delta_hatX(self, module, quant_input_activation, original_input_activation):
+            c = super().calculate_delta_hatX(module, quant_input_activation, original_input_activation)
+            cs[self.module_to_name[module]] = c.clone()
+            return c
+
+    qz = Recording(**quantizer_kw)
+    try:
+        ref_generic.run_quantize_with_qep(
+            model_config=_FakeModelConfig(model), quantizer=qz,
+            qep_config=QEPConfig(general=True, device="cpu", percdamp=0.01, perccorr=0.5),
+            calibration_config=None, report_progress=False)
+    finally:
+        ref_generic.prepare_calibration_dataset = original
+    out = {"ids": ids.numpy(), "order": np.array(order), "results": np.array(list(qz.results))}
+    out.update(extra)
+    for name, p in model.state_dict().items():
+        out[f"final/{name}"] = _np(p.detach().cpu())
+    for name in order:
+        out[f"H/{name}"] = hs[name].numpy()
+        if name in cs:
+            out[f"C/{name}"] = cs[name].numpy()
+    for name, r in qz.results.items():
+        out[f"qweight/{name}"] = r.qweight.numpy()
+        out[f"qzeros/{name}"] = _np(r.qzeros)
+        out[f"scales/{name}"] = _np(r.scales)
+        out[f"packed/{name}"] = np.int64(bool(r.qweight_is_packed))
+    np.savez_compressed(os.path.join(HERE, f"driver_{tag}.npz"), **out)
+
+
 def driver_fixtures(ref_gptq, ref_arch):
     """Block-wise QEP driver of the reference on the seeded toy models of tests/toy_models.py."""
     sys.path.insert(0, os.path.dirname(HERE))
@@ -357,6 +456,10 @@ def driver_fixtures(ref_gptq, ref_arch):
         model = toy_models.tiny_llama(seed=0)
         init = {f"init/{k}": _np(v.detach().clone()) for k, v in model.state_dict().items()}
         _run_reference_driver(ref_gptq, ref_arch, model, toy_models.llama_ids(0), kw, tag, extra=init)
+    model = toy_models.tiny_llama(seed=0)
+    init = {f"init/{k}": _np(v.detach().clone()) for k, v in model.state_dict().items()}
+    _run_reference_generic_driver(ref_gptq, model, toy_models.llama_ids(0), dict(wbits=4, groupsize=32, sym=False),
+                                  "generic_llama_b4", init)
     model = toy_models.routed_moe(seed=0)
     init = {f"init/{k}": _np(v.detach().clone()) for k, v in model.state_dict().items()}
     _run_reference_driver(ref_gptq, ref_arch, model, toy_models.moe_ids(0),

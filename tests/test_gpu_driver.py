@@ -780,6 +780,27 @@ def test_gpt_oss_layer_unfused_bf16_through_the_driver():
     assert total > 0 and matched / total >= 0.99, matched / total
     for m, name in q.module_to_name.items():
         assert m.weight.dtype == torch.bfloat16
+    # the way back for the save path: the quantized experts in the fused layout of the checkpoint
+    from onecompression_b200.utils import fuse_moe_experts
+
+    routed = layer.mlp.experts
+    want = [(e.gate_proj.weight.data.clone(), e.up_proj.weight.data.clone(), e.down_proj.weight.data.clone(),
+             e.down_proj.bias.data.clone()) for e in routed.experts]
+    x = torch.randn(20, 128, device=DEV).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(4, device=DEV)[:2] for _ in range(20)])
+    wts = torch.rand(20, 2, device=DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        y_routed = routed(x, router_indices=idx, routing_weights=wts)
+    assert fuse_moe_experts(layer) == 1
+    fused = layer.mlp.experts
+    assert fused.gate_up_proj.shape == (4, 128, 256) and fused.gate_up_proj.dtype == torch.bfloat16
+    for e, (gw, uw, dw, db) in enumerate(want):
+        assert torch.equal(fused.gate_up_proj.data[e, :, 0::2], gw.t())
+        assert torch.equal(fused.gate_up_proj.data[e, :, 1::2], uw.t())
+        assert torch.equal(fused.down_proj.data[e], dw.t()) and torch.equal(fused.down_proj_bias.data[e], db)
+    with torch.no_grad():
+        y_fused = fused(x, router_indices=idx, routing_weights=wts)
+    assert torch.allclose(y_fused.float(), y_routed.float(), rtol=5e-2, atol=5e-2)
 
 
 @pytest.mark.parametrize("act,pack,bits", [(False, True, 4), (True, True, 3), (False, False, 5)])

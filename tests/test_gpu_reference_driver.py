@@ -316,3 +316,69 @@ def test_expert_hessians_and_fallbacks_against_reference_driver():
         p = plain.results[name]
         assert torch.equal(p.qweight, r.qweight) and torch.equal(p.scales, r.scales) \
             and torch.equal(p.qzeros, r.qzeros), name
+
+
+def test_generic_driver_follows_reference_generic_driver():
+    """The architecture-independent driver (reference run_quantize_with_qep,
+    onecomp/qep/_quantize_with_qep.py:35-133): one forward pass per layer, every layer forms its own
+    H (slices of eight sequences) and C from captured activations through
+    Quantizer.calculate_hessian / calculate_delta_hatX.  Same comparison as for the block-wise driver:
+    after each layer the run continues with the weight the reference installed."""
+    from onecompression_b200 import GPTQ, QEPConfig
+    from onecompression_b200.qep import run_quantize_with_qep
+
+    z = load_golden("driver_generic_llama_b4.npz")
+    kw = LLAMA_CASES["llama_b4"]
+    order, hs, cs = [], {}, {}
+
+    class Spy(GPTQ):
+        def calculate_hessian(self, module, input):  # pylint: disable=redefined-builtin
+            h, n = super().calculate_hessian(module, input)
+            name = self.module_to_name[module]
+            if name not in hs:
+                order.append(name)
+                hs[name] = h.detach().cpu().clone()
+            return h, n
+
+        def calculate_delta_hatX(self, module, quant_input_activation, original_input_activation):
+            c = super().calculate_delta_hatX(module, quant_input_activation, original_input_activation)
+            cs[self.module_to_name[module]] = c.detach().cpu().clone()
+            return c
+
+        def quantize_with_qep(self, module, *a, **k):
+            out = super().quantize_with_qep(module, *a, **k)
+            name = self.module_to_name[module]
+            forced = f16(z[f"final/{name}.weight"]).reshape(z[f"init/{name}.weight"].shape)
+            self.results[name].__dict__["_device_dequantized"] = forced.to(module.weight.device)
+            return out
+
+    spy = Spy(**kw)
+    model = _load_model(z, toy_models.tiny_llama).to(DEV)
+    ids = torch.from_numpy(z["ids"]).to(DEV)
+    run_quantize_with_qep(None, spy, QEPConfig(general=True, device=DEV, percdamp=0.01, perccorr=0.5), None,
+                          model=model, model_inputs={"input_ids": ids}, report_progress=False, batch_size=16)
+    assert order == [str(n) for n in z["order"]]
+    assert sorted(spy.results) == sorted(str(n) for n in z["results"])
+    same = total = 0
+    for name in order:
+        blk = int(name.split(".")[2])
+        assert (name in cs) == (f"C/{name}" in z), name                 # mlp.down_proj: no correction
+        eh = _rel(hs[name], z[f"H/{name}"])
+        ec = _rel(cs[name], z[f"C/{name}"]) if name in cs else None
+        eq = _our_codes(spy.results[name]) == _ref_codes(z, name, kw["wbits"])
+        same += int(eq.sum())
+        total += eq.size
+        print(f"[generic] {name}: H rel {eh:.2e}, C rel {'-' if ec is None else f'{ec:.2e}'}, codes {eq.mean():.5f}")
+        assert eh < (2e-5 if (".layers.0.self_attn." in name) else 1e-4 if blk == 0 else 5e-4), (name, eh)
+        if ec is not None:
+            if not np.any(z[f"C/{name}"]):
+                assert ec == 0.0, name
+            else:
+                assert ec < (1e-3 if blk == 0 else 5e-3), (name, ec)
+        assert eq.mean() >= 0.99, (name, eq.mean())
+    print(f"[generic] identical codes {same / total:.5f}")
+    assert same / total >= 0.995
+    # the model holds the forced (= the reference's) weights now
+    for name in order:
+        mod = dict(model.named_modules())[name]
+        assert np.array_equal(bits16(mod.weight.data).reshape(-1), z[f"final/{name}.weight"].reshape(-1))

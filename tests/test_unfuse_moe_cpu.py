@@ -2,7 +2,7 @@
 
 import torch
 
-from onecompression_b200.utils import RoutedExperts, unfuse_moe_experts
+from onecompression_b200.utils import RoutedExperts, fuse_moe_experts, unfuse_moe_experts
 
 
 def _tiny_gpt_oss():
@@ -44,3 +44,37 @@ def test_unfused_experts_compute_the_same_function():
     assert sum(n for _, n in calls) == 80                           # every (token, slot) pair exactly once
     names = [n for n, m in layer.named_modules() if isinstance(m, torch.nn.Linear) and "experts" in n]
     assert len(names) == 12 and "mlp.experts.experts.2.down_proj" in names
+
+
+def test_fusing_back_restores_the_fused_layout():
+    """un-fuse -> fuse gives back the very tensors (layout of the reference's _fuse_gpt_oss_one,
+    onecomp/utils/unfuse_moe.py:499-574: gate / up interleaved, down transposed) and the same
+    function; a changed expert weight lands at its place in the fused tensors."""
+    _cfg, layer = _tiny_gpt_oss()
+    fused = layer.mlp.experts
+    before = {k: getattr(fused, k).data.clone() for k in
+              ("gate_up_proj", "gate_up_proj_bias", "down_proj", "down_proj_bias")}
+    x = torch.randn(24, 64)
+    idx = torch.stack([torch.randperm(4)[:2] for _ in range(24)])
+    w = torch.rand(24, 2)
+    with torch.no_grad():
+        want = fused(x, router_indices=idx, routing_weights=w)
+    assert unfuse_moe_experts(layer) == 1
+    layer.mlp.experts[2].up_proj.weight.data[5, 7] = 3.0          # stands for a quantized weight
+    assert fuse_moe_experts(layer) == 1
+    again = layer.mlp.experts
+    assert type(again).__name__ == "GptOssExperts"
+    assert sorted(k for k, _ in again.named_parameters()) == sorted(before)
+    for k, v in before.items():
+        got = getattr(again, k).data
+        assert got.shape == v.shape and got.dtype == v.dtype
+        if k == "gate_up_proj":
+            assert got[2, 7, 2 * 5 + 1] == 3.0                    # up = odd columns; [expert, in, 2*out+1]
+            got = got.clone()
+            got[2, 7, 2 * 5 + 1] = v[2, 7, 2 * 5 + 1]
+        assert torch.equal(got, v), k
+    layer.mlp.experts.gate_up_proj.data[2, 7, 11] = before["gate_up_proj"][2, 7, 11]
+    with torch.no_grad():
+        got = layer.mlp.experts(x, router_indices=idx, routing_weights=w)
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+    assert fuse_moe_experts(layer) == 0
