@@ -53,9 +53,16 @@ def _peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             p = json.load(f)
-        return {"tflops": float(p["bf16_tflops"]), "hbm": float(p["hbm_gbs"]), "src": "measured"}
+        return {"tflops": float(p["bf16_tflops"]), "hbm": float(p["hbm_gbs"]), "src": "measured",
+                "sustained": float(p.get("bf16_tflops_sustained", 0.0)) or None}
     except Exception:  # pylint: disable=broad-except
-        return {"tflops": 1590.0, "hbm": 6650.0, "src": "fallback"}
+        return {"tflops": 1590.0, "hbm": 6650.0, "src": "fallback", "sustained": 1400.0}
+
+
+def _sustained(peaks):
+    """The library GEMM's throughput in a seconds-long loop under the power cap (what a kernel inside a
+    long step can be compared with)."""
+    return peaks.get("sustained") or peaks["tflops"]
 
 
 class ClockSampler:
@@ -132,8 +139,10 @@ class HostStreams:
                     self.ready[key].append(self.up.record_event())
 
     def _wait(self, key, first, size):
+        # the stream that is about to read (the driver may run the block on a stream of its own)
+        reader = torch.cuda.current_stream()
         for c in range(first // self.chunk, (first + size - 1) // self.chunk + 1):
-            self.main.wait_event(self.ready[key][c])
+            reader.wait_event(self.ready[key][c])
 
     def before_read_f(self, first, size):
         self._wait("f", first, size)
@@ -142,7 +151,7 @@ class HostStreams:
         self._wait("q", first, size)
 
     def _download(self, key, first, size, tensor):
-        self.down.wait_event(self.main.record_event())
+        self.down.wait_event(torch.cuda.current_stream().record_event())
         with torch.cuda.stream(self.down):
             self.host[key][first:first + size].copy_(tensor[first:first + size], non_blocking=True)
 
@@ -307,6 +316,25 @@ def run_ours(args):
     algorithmic = 2 * 2.0 * ntok * d * d
     peaks = _peaks()
     achieved = executed / (k_ms * 1e-3) / 1e12
+    del acc
+    # the same kernel on the widest Hessian of the workload (down_proj, d = 14336, H only): 58 % of a
+    # step's moment flops
+    d14 = shape["intermediate_size"]
+    x14 = torch.randn(ntok, d14, device=dev, dtype=torch.float16)
+    acc = kernels.MomentAccumulator(d14, dev, cross=False)
+    for _ in range(2):
+        acc.add(x14)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(3):
+        acc.add(x14)
+    e1.record()
+    torch.cuda.synchronize()
+    acc.finalize()
+    k14_ms = e0.elapsed_time(e1) / 3
+    tiles14 = sum(d14 // 256 - (tm >> 1) for tm in range(d14 // 128))
+    achieved14 = tiles14 * 128 * 256 * 2.0 * ntok / (k14_ms * 1e-3) / 1e12
+    del x14
 
     del stack, host_blocks, acc, xq, xf
     kernels.release_workspaces()
@@ -342,14 +370,17 @@ def run_ours(args):
             "kernel": "moment_tc_kernel (H + C, d=4096, %d tokens per launch)" % ntok,
             "bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["tflops"],
             "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4),
-            # DRAM bytes per launch: the ncu capture of the 16384-token case (1.10 GB read + write,
+            # DRAM bytes per launch: the ncu capture of the 16384-token case (1.41 GB read + write,
             # of which 0.20 GB are the token-independent H and C tiles) scaled to this launch's tokens
-            "traffic": round(0.20e9 + 0.90e9 * ntok / 16384),
+            "traffic": round(0.20e9 + 1.21e9 * ntok / 16384),
             "traffic_note": "scaled from the ncu capture of a 16384-token launch (profiles/)",
             "peak_source": peaks["src"] + " (burst: kernel timed alone)",
             "flops": "executed MMA flops (upper tiles of H, all of C twice: two 16-bit terms of Xf - Xq)",
             "hessian_gemm_tflops_algorithmic": round(algorithmic / (k_ms * 1e-3) / 1e12, 1),
             "ms_per_launch": round(k_ms, 4),
+            "d14336_h_only": {"ms_per_launch": round(k14_ms, 4), "achieved": round(achieved14, 1),
+                              "frac": round(achieved14 / peaks["tflops"], 4), "tokens": ntok},
+            "frac_of_sustained_peak": round(achieved / _sustained(peaks), 4),
         },
     }
     if parity is not None:
@@ -753,6 +784,13 @@ def run_profile_case(case: str):
         for _ in range(3):
             acc.add(xq, xf)
         acc.finalize()
+    elif case == "moment14336":
+        d, ntok = 14336, 8192                     # X is 235 MB (above L2), H 822 MB
+        xq = torch.randn(ntok, d, generator=g, device=dev, dtype=torch.float16)
+        acc = kernels.MomentAccumulator(d, dev, cross=False)
+        for _ in range(3):
+            acc.add(xq)
+        acc.finalize()
     elif case in ("column", "factor", "qep"):
         out = 4096
         x = torch.randn(16384, d, generator=g, device=dev, dtype=torch.float16)
@@ -781,7 +819,7 @@ def main():
                     help="leave out the other configurations and the same-box library baselines")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="profiling aid: leave out the host-buffer pass (the line then has no e2e value)")
-    ap.add_argument("--profile-case", default=None, choices=["moment", "column", "factor", "qep"],
+    ap.add_argument("--profile-case", default=None, choices=["moment", "moment14336", "column", "factor", "qep"],
                     help="run one small kernel case for an ncu capture instead of the benchmark")
     args = ap.parse_args()
     if args.profile_case:

@@ -438,8 +438,15 @@ class BlockQuantizer:
     def __init__(self, quantizer: Quantizer, qep_config: QEPConfig, batch_size: int, device,
                  dist=None, cache_budget_bytes: Optional[int] = None, memoize: bool = True,
                  profile: bool = False, fuse_rmsnorm: bool = True, fuse_elementwise: bool = True,
-                 stack_layers: bool = True):
+                 stack_layers: bool = True, high_priority: bool = True):
         self.memoize = memoize
+        # The block's own chain of kernels runs on a high-priority stream; the prefetched
+        # full-precision pass of the next block (``prefetch``) runs on a normal-priority side
+        # stream.  The block scheduler then gives SMs to the chain first, and the side stream's
+        # kernels fill the SMs the latency-bound phases (factorisation, column loop) leave idle
+        # instead of competing with the throughput-bound ones.
+        self.high_priority = high_priority
+        self._main = None
         # Llama-style RMSNorm modules of the block run as one kernel during the passes (same
         # rounding points as the module; the row sum is formed in another order)
         self.fuse_rmsnorm = fuse_rmsnorm
@@ -604,7 +611,18 @@ class BlockQuantizer:
         self._stream_io = stream_io
         try:
             with kernels.deferred_host_copies():
-                return self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+                if not self.high_priority or self.profile:
+                    return self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+                caller = torch.cuda.current_stream(self.device)
+                if self._main is None:
+                    self._main = torch.cuda.Stream(self.device, priority=-1)     # lower number: higher priority
+                self._main.wait_stream(caller)
+                with torch.cuda.stream(self._main):
+                    next_q, next_f = self._run_block(block_q, inps_q, inps_f, kwargs, on_layer_done, next_block)
+                caller.wait_stream(self._main)
+                for t in (next_q, next_f):
+                    t.record_stream(caller)
+                return next_q, next_f
         finally:
             self._stream_io = None
 
