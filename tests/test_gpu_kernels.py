@@ -542,3 +542,25 @@ def test_all_zero_weight_rows_through_the_column_loop(K):
             assert torch.equal(out["scales"].cpu()[:, r], ref["scales"][:, r])
             assert torch.all(out["scales_f32"].cpu()[:, r] == 2.0 / 15.0)
             assert not out["dequantized"][r].any()
+
+
+def test_column_loop_does_not_depend_on_rows_per_cta(K):
+    """The kernel picks 32, 64, 128 or 256 rows per CTA from the layer's row count, and CTAs with few
+    rows hand work to helper threads; a row's result must not depend on any of that (this is what
+    makes stacked layers, batched experts and row slabs on several GPUs bit-identical to the plain
+    call).  19200 rows run with 256 rows per CTA, their halves with 128, a 4096-row slab with 32."""
+    g = torch.Generator(device=dev()).manual_seed(77)
+    d, out = 512, 19200
+    x = torch.randn(4096, d, generator=g, device=dev()).half()
+    x[:, ::37] *= 6
+    h, _ = K.hessian_from_activations(x)
+    w = (torch.randn(out, d, generator=g, device=dev()) * 0.02).half()
+    for act, gs in ((False, 128), (True, 32)):
+        fac = K.factor_hessian(h, 0.01, act)
+        whole = K.gptq_quantize(w, fac, wbits=3, groupsize=gs, sym=False, want_codes=True)
+        for r0, r1 in ((0, 9600), (9600, 19200), (1024, 5120), (7000 // 32 * 32, 7000 // 32 * 32 + 64)):
+            part = K.gptq_quantize(w[r0:r1].contiguous(), fac, wbits=3, groupsize=gs, sym=False, want_codes=True)
+            assert torch.equal(part["codes"], whole["codes"][r0:r1]), (act, r0, r1)
+            assert torch.equal(part["scales"], whole["scales"][:, r0:r1])
+            assert torch.equal(part["dequantized"], whole["dequantized"][r0:r1])
+            assert torch.equal(part["qweight"], whole["qweight"][:, r0:r1])
