@@ -222,6 +222,7 @@ _GATED_MLP_BODY = (
     "return down_proj",
 )
 _source_checks: dict = {}
+_declined_logged: set = set()
 
 
 def _code_lines(fn):
@@ -286,10 +287,33 @@ class _FusedOps:
                     self.norm_mods.append(m)
                 elif elementwise and _is_plain_gated_mlp(m):
                     self.mlp_mods.append(m)
+                else:
+                    self._note_declined(m, norms, elementwise)
                 if elementwise and hasattr(m, "q_proj") and hasattr(m, "k_proj"):
                     ns = _plain_rope_namespace(m)
                     if ns is not None and all(ns is not x for x, _ in self.rope_spaces):
                         self.rope_spaces.append((ns, ns.apply_rotary_pos_emb))
+                    elif ns is None:
+                        self._say_once(("rope", type(m)), "rotary embedding of %s is not the recognised "
+                                       "formulation: it runs the model's own operators", type(m).__name__)
+
+    @staticmethod
+    def _say_once(key, message, *args):
+        """One log line per module class whose code is not recognised: the passes then run the model's
+        own elementwise operators for it (same results, more kernels - e.g. after a transformers
+        release that rewords a forward)."""
+        if key not in _declined_logged:
+            _declined_logged.add(key)
+            logger.info("fused block operators: " + message, *args)
+
+    def _note_declined(self, m, norms, elementwise):
+        name = type(m).__name__.lower()
+        if norms and "rmsnorm" in name and getattr(m, "weight", None) is not None:
+            self._say_once(("norm", type(m)), "%s is not the recognised RMSNorm (fp32 statistics, downcast, "
+                           "weight product; fp16 weight): it runs the model's own operators", type(m).__name__)
+        elif elementwise and all(hasattr(m, a) for a in ("gate_proj", "up_proj", "down_proj")):
+            self._say_once(("mlp", type(m)), "%s is not the recognised gated MLP (down(act(gate(x)) * up(x)) with "
+                           "SiLU): it runs the model's own operators", type(m).__name__)
 
     def __enter__(self):
         for m in self.norm_mods:

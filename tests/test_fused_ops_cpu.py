@@ -67,3 +67,33 @@ def test_other_formulations_are_left_alone():
     ops = _FusedOps([llama])
     assert len(ops.norm_mods) == 1 and len(ops.mlp_mods) == 0       # only post_attention_layernorm is left
     assert len(_FusedOps([llama], norms=False, elementwise=False).norm_mods) == 0
+
+
+def test_unrecognised_modules_are_reported_once(caplog):
+    """A module that looks like a fusable operator but whose code differs (another formulation, or a
+    library release that rewords a forward) is named in the log once, so the extra kernels of the
+    model's own operators do not go unnoticed."""
+    import logging
+
+    from onecompression_b200.qep import _quantize_with_qep_arch as arch
+
+    llama, _ = _blocks()
+
+    class ReworkedRMSNorm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(64).half())
+            self.variance_epsilon = 1e-6
+
+        def forward(self, x):
+            v = x.float().pow(2).mean(-1, keepdim=True)
+            return (self.weight * (x.float() * torch.rsqrt(v + self.variance_epsilon))).to(x.dtype)
+
+    llama.input_layernorm = ReworkedRMSNorm()
+    arch._declined_logged.clear()
+    with caplog.at_level(logging.INFO, logger=arch.logger.name):
+        first = _FusedOps([llama])
+        _FusedOps([llama])
+    assert len(first.norm_mods) == 1
+    lines = [r.getMessage() for r in caplog.records if "ReworkedRMSNorm" in r.getMessage()]
+    assert len(lines) == 1 and "model's own operators" in lines[0]
