@@ -253,6 +253,11 @@ int oc_gemm_f32(const float* A, long long lda, const float* B, long long ldb, fl
  * of the tensor-core engine expired on the current device (201..205). */
 int oc_set_gemm_engine(int mode);
 int oc_gemm_tc_status(void);
+/* Output tile of the tensor-core engine for plain products (flags == 0): 0 (default) picks
+ * 128x128 or 128x256 tiles per product by the number of waves of tiles over the SMs, 1 forces
+ * 128x128, 2 forces 128x256.  Both cut k into the same accumulation chains, so the result bits do
+ * not depend on the choice.  Returns the previous setting. */
+int oc_set_gemm_tile_shape(int mode);
 
 #ifdef __cplusplus
 }

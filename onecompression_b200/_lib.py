@@ -44,6 +44,7 @@ SIGNATURES = {
     "oc_dequantize_packed": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _L, _P]),
     "oc_gemm_f32": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _F, _I, _I, _I, _P]),
     "oc_set_gemm_engine": (_I, [_I]),
+    "oc_set_gemm_tile_shape": (_I, [_I]),
     "oc_gemm_tc_status": (_I, []),
 }
 

@@ -6,15 +6,22 @@
 // dropped lo*lo term and the truncation of lo to tf32 are about 2^-22 relative, i.e. the
 // result is an fp32-grade product sum.
 //
-// Pipeline of one persistent CTA (128 x 128 output tiles, 32 k-values per stage, 3 stages):
-//   warp 0      TMA: raw fp32 tiles of A and B into shared memory (128-byte swizzle)
-//   warps 2..5  split: rewrite every raw value in place as hi and store lo at the same
-//               offset of a second buffer (elementwise, so the swizzled layout is kept)
-//   warp 1      MMA: per 8 k-values three tcgen05.mma (lo*hi, hi*lo, hi*hi), M=128 N=128 K=8
-//   warps 6..9  drain: accumulators leave TMEM every `chunk_k` k-values and are summed in
-//               registers (the tensor core truncates when it accumulates, so chains are kept
-//               short); at the end of a tile alpha / beta are applied and C is written while
-//               the MMA warp already works on the next tile in the other TMEM buffer.
+// Pipeline of one persistent CTA:
+//   warp 0      TMA: raw fp32 tiles of A and B into shared memory (swizzled)
+//   split warps rewrite every raw value in place as hi and store lo at the same offset of a
+//               second buffer (elementwise, so the swizzled layout is kept)
+//   warp 1      MMA: per 8 k-values three tcgen05.mma (lo*hi, hi*lo, hi*hi), M=128 N=BN K=8
+//   drain warps accumulators leave TMEM every 256 k-values and are summed in registers (the
+//               tensor core truncates when it accumulates, so chains are kept short); at the
+//               end of a tile alpha / beta are applied and C is written while the MMA warp
+//               already works on the next tile in the other TMEM buffer.
+// Two tile shapes share the code.  Narrow: 128 x 128 tiles, 32 k-values per stage, 3 stages,
+// 4 split and 4 drain warps.  Wide: 128 x 256 tiles, 16 k-values per stage, 4 stages, 4 split
+// and 8 drain warps.  The kernel is bound by shared-memory bandwidth (TMA write, split read
+// and two writes, three operand reads per MMA pair); per flop a wide tile reads the operands
+// 1.5 instead of 2 times, so it is chosen when the product has enough tiles to fill the SMs.
+// Both shapes cut k into the same 256-wide chains, so a plain product gives the same bits
+// with either.
 // Operands may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major); both are
 // native tcgen05 layouts, so the four transpose combinations need no data movement.
 // All mbarrier waits are bounded (see tc_common.cuh).
@@ -24,12 +31,28 @@ namespace {
 
 using namespace octc;
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
-constexpr int OPER_BYTES = BM * BK * 4;                 // 16 KB: one operand tile (hi or lo)
-constexpr int STAGE_BYTES = 4 * OPER_BYTES;             // A hi, A lo, B hi, B lo
-constexpr int SMEM_DYN = STAGES * STAGE_BYTES + 1024;
-constexpr int NUM_THREADS = 320;
-constexpr int N_SPLIT_THREADS = 128;
+constexpr int BM = 128;
+constexpr int CHAIN_K = 128;                            // k-values per accumulation chain (48 MMAs)
+
+template <int BN_, int BK_, int STAGES_, int FIRST_SPLIT_>
+struct Shape {
+  static constexpr int BN = BN_, BK = BK_, STAGES = STAGES_, SPLIT_WARPS = 4, FIRST_SPLIT = FIRST_SPLIT_;
+  static constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;   // one operand tile (hi or lo)
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);          // A hi, A lo, B hi, B lo
+  static constexpr int SMEM_DYN = STAGES * STAGE_BYTES + 1024;
+  static constexpr int DRAIN_WARPS = 4 * (BN / 128);
+  static constexpr int FIRST_DRAIN = FIRST_SPLIT + SPLIT_WARPS;
+  // With 16 warps the register file gives 128 registers per thread at launch, fewer than a drain
+  // thread needs for its 128 partial sums: the warpgroups then trade registers (setmaxnreg).
+  static constexpr bool TRADE_REGISTERS = FIRST_SPLIT == 4;
+  static constexpr int THREADS = 32 * (FIRST_DRAIN + DRAIN_WARPS);
+  static constexpr int SPLIT_THREADS = 32 * SPLIT_WARPS;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static_assert(BK == 32 || BK == 16, "K-major rows are one 128- or 64-byte swizzle span");
+  static_assert(BN == 128 || BN == 256, "one or two 128-column halves");
+};
+using Narrow = Shape<128, 32, 3, 2>;   // warps: TMA, MMA, 4 split, 4 drain
+using Wide = Shape<256, 16, 4, 4>;     // warps: TMA, MMA, 2 idle | 4 split | 8 drain (four warpgroups)
 
 struct TcGemmParams {
   float* C; long long ldc; long long strideC;
@@ -37,39 +60,47 @@ struct TcGemmParams {
   float alpha, beta;
   int flags, batch;
   int tiles_m, tiles_n;
-  int chunk_stages;
   int* status;
 };
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN>
 __host__ __device__ constexpr uint32_t idesc() {
   // c = f32 (1<<4); a, b = tf32 (2<<7, 2<<10); major bits 15 / 16; N>>3 at 17; M>>4 at 24
   return (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-// K-major tile: 128 rows (M or N index) of 128 bytes (32 k-values), SWIZZLE_128B;
-//   groups of 8 rows 1024 bytes apart; the next 8 k-values are 32 bytes further in the row.
-// MN-major tile: four 32-column atoms of [32 k-rows x 128 bytes], 4096 bytes apart.  32-bit
+// K-major tile: rows (M or N index) of BK k-values = one swizzle span (128 bytes for BK 32,
+//   64 bytes for BK 16); groups of 8 rows are 8 spans apart; the next 8 k-values are 32 bytes
+//   further in the row.
+// MN-major tile: 32-column atoms of [BK k-rows x 128 bytes], one after another.  32-bit
 //   MN-major operands exist only in the "128-byte swizzle, 32-byte atom" layout (TMA mode
 //   SWIZZLE_128B_ATOM_32B): the pattern repeats every 4 k-rows (512 bytes), an MMA of 8
 //   k-values spans two such groups, the next 8 k-values start 1024 bytes further.
-template <bool MN>
+template <bool MN, int BK>
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, int k8) {
   uint64_t d;
   if (MN) {
     d = (uint64_t)(((addr + k8 * 1024) & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(4096 >> 4) << 16;   // leading offset: next 32-column atom
-    d |= (uint64_t)(512 >> 4) << 32;    // stride offset: next group of 4 k-rows
-    d |= 1ull << 61;                    // 128-byte swizzle with 32-byte atoms (the MN-major tf32 layout)
+    d |= (uint64_t)((BK * 128) >> 4) << 16;   // leading offset: next 32-column atom
+    d |= (uint64_t)(512 >> 4) << 32;          // stride offset: next group of 4 k-rows
+    d |= 1ull << 61;                          // 128-byte swizzle with 32-byte atoms (the MN-major tf32 layout)
   } else {
     d = (uint64_t)(((addr + k8 * 32) & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;             // unused for swizzled K-major layouts
-    d |= (uint64_t)(1024 >> 4) << 32;   // next group of 8 rows
-    d |= 2ull << 61;                    // 128-byte swizzle
+    d |= (uint64_t)1 << 16;                   // unused for swizzled K-major layouts
+    d |= (uint64_t)((8 * BK * 4) >> 4) << 32; // next group of 8 rows
+    d |= (BK == 32 ? 2ull : 4ull) << 61;      // 128-byte / 64-byte swizzle
   }
   d |= 1ull << 46;
   return d;
+}
+
+// The tensor core reads the upper 19 bits of a 32-bit operand (sign, exponent, 10 mantissa bits),
+// so the raw value serves as hi = trunc(v) without being rewritten.  lo = v - hi is exact; half a
+// tf32 unit is added to its magnitude so that the tensor core's truncation rounds it to nearest.
+__device__ __forceinline__ float split_lo(float v) {
+  const float l = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+  return __uint_as_float(__float_as_uint(l) + 0x1000u);
 }
 
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t id,
@@ -80,17 +111,18 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(accumulate) : "memory");
 }
 
-template <bool MN>
+template <bool MN, int ROWS, int BK>
 __device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, int mn0, int k0,
                                              int batch, uint32_t bar) {
   if (MN) {
 #pragma unroll
-    for (int a = 0; a < BM / 32; ++a) tma_load_3d(dst + a * 4096, map, mn0 + a * 32, k0, batch, bar);
+    for (int a = 0; a < ROWS / 32; ++a) tma_load_3d(dst + a * BK * 128, map, mn0 + a * 32, k0, batch, bar);
   } else {
     tma_load_3d(dst, map, k0, mn0, batch, bar);
   }
 }
 
+template <int BN, int BK>
 __device__ __forceinline__ bool tile_coords(const TcGemmParams& p, int item, int& z, int& m0, int& n0,
                                             int& k_lo, int& k_hi) {
   const int per = p.tiles_m * p.tiles_n;
@@ -108,10 +140,12 @@ __device__ __forceinline__ bool tile_coords(const TcGemmParams& p, int item, int
   return true;
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <bool A_MN, bool B_MN, class S>
+__global__ void __launch_bounds__(S::THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const TcGemmParams p) {
+  constexpr int BN = S::BN, BK = S::BK, STAGES = S::STAGES, STAGE_BYTES = S::STAGE_BYTES;
+  constexpr int A_BYTES = S::A_BYTES, B_BYTES = S::B_BYTES, CHAIN_STAGES = CHAIN_K / BK;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_raw[STAGES], bar_split[STAGES], bar_empty[STAGES];
   __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
@@ -126,16 +160,17 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_raw[s]), 1);
-      mbar_init(smem_u32(&bar_split[s]), N_SPLIT_THREADS);
+      mbar_init(smem_u32(&bar_split[s]), S::SPLIT_THREADS);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), S::DRAIN_WARPS); }
     abort_flag_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(&tmem_slot)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -144,21 +179,23 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const uint32_t tmem_base = tmem_slot;
   const int total_items = p.batch * p.tiles_m * p.tiles_n;
 
+  if (warp < S::FIRST_SPLIT) {
+  if (S::TRADE_REGISTERS) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {
       uint32_t stage = 0, phase = 1;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         int z, m0, n0, k_lo, k_hi;
-        if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+        if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
         for (int k0 = k_lo; k0 < k_hi; k0 += BK) {
           ok = mbar_wait(smem_u32(&bar_empty[stage]), phase, abort_flag, p.status, 201);
           if (!ok) break;
           const uint32_t bar = smem_u32(&bar_raw[stage]);
           const uint32_t sa = stage_base + stage * STAGE_BYTES;
-          mbar_expect_tx(bar, 2 * OPER_BYTES);
-          load_operand<A_MN>(sa, &map_a, m0, k0, z, bar);
-          load_operand<B_MN>(sa + 2 * OPER_BYTES, &map_b, n0, k0, z, bar);
+          mbar_expect_tx(bar, A_BYTES + B_BYTES);
+          load_operand<A_MN, BM, BK>(sa, &map_a, m0, k0, z, bar);
+          load_operand<B_MN, BN, BK>(sa + 2 * A_BYTES, &map_b, n0, k0, z, bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -170,32 +207,32 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t ID = idesc<A_MN, B_MN>();
+      constexpr uint32_t ID = idesc<A_MN, B_MN, BN>();
       uint32_t stage = 0, phase = 0, cc = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         int z, m0, n0, k_lo, k_hi;
-        if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+        if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
         const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
-        const int n_chunks = max(1, (n_stages + p.chunk_stages - 1) / p.chunk_stages);
+        const int n_chunks = max(1, (n_stages + CHAIN_STAGES - 1) / CHAIN_STAGES);
         for (int ch = 0; ch < n_chunks && ok; ++ch, ++cc) {
           const uint32_t buf = cc & 1u;
           ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), ((cc >> 1) & 1u) ^ 1u, abort_flag, p.status, 202);
           if (!ok) break;
           tc_fence_after();
-          const int s_begin = ch * p.chunk_stages;
-          const int s_end = min(n_stages, s_begin + p.chunk_stages);
+          const int s_begin = ch * CHAIN_STAGES;
+          const int s_end = min(n_stages, s_begin + CHAIN_STAGES);
           const uint32_t tmem_d = tmem_base + buf * BN;
           for (int s = s_begin; s < s_end; ++s) {
             ok = mbar_wait(smem_u32(&bar_split[stage]), phase, abort_flag, p.status, 203);
             if (!ok) break;
             tc_fence_after();
             const uint32_t a_hi = stage_base + stage * STAGE_BYTES;
-            const uint32_t a_lo = a_hi + OPER_BYTES, b_hi = a_hi + 2 * OPER_BYTES, b_lo = a_hi + 3 * OPER_BYTES;
+            const uint32_t a_lo = a_hi + A_BYTES, b_hi = a_hi + 2 * A_BYTES, b_lo = b_hi + B_BYTES;
 #pragma unroll
             for (int k8 = 0; k8 < BK / 8; ++k8) {
-              const uint64_t dah = make_desc<A_MN>(a_hi, k8), dal = make_desc<A_MN>(a_lo, k8);
-              const uint64_t dbh = make_desc<B_MN>(b_hi, k8), dbl = make_desc<B_MN>(b_lo, k8);
+              const uint64_t dah = make_desc<A_MN, BK>(a_hi, k8), dal = make_desc<A_MN, BK>(a_lo, k8);
+              const uint64_t dbh = make_desc<B_MN, BK>(b_hi, k8), dbl = make_desc<B_MN, BK>(b_lo, k8);
               umma_tf32(tmem_d, dal, dbh, ID, (s > s_begin || k8 > 0) ? 1u : 0u);
               umma_tf32(tmem_d, dah, dbl, ID, 1u);
               umma_tf32(tmem_d, dah, dbh, ID, 1u);
@@ -208,32 +245,31 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  }  // further warps of the first warpgroup (wide shape) idle
+  } else if (warp < S::FIRST_DRAIN) {
     // split warps
-    const int st = tid - 64;  // 0..127
+    if (S::TRADE_REGISTERS) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    const int st = tid - 32 * S::FIRST_SPLIT;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       int z, m0, n0, k_lo, k_hi;
-      if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+      if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
       for (int k0 = k_lo; k0 < k_hi; k0 += BK) {
         ok = mbar_wait(smem_u32(&bar_raw[stage]), phase, abort_flag, p.status, 204);
         if (!ok) break;
         uint8_t* base = stage_ptr + stage * STAGE_BYTES;
 #pragma unroll
         for (int op = 0; op < 2; ++op) {
-          float4* hi = reinterpret_cast<float4*>(base + op * 2 * OPER_BYTES);
-          float4* lo = reinterpret_cast<float4*>(base + op * 2 * OPER_BYTES + OPER_BYTES);
-#pragma unroll
-          for (int i = 0; i < OPER_BYTES / 16 / N_SPLIT_THREADS; ++i) {
-            const int idx = i * N_SPLIT_THREADS + st;
+          const int bytes = op ? B_BYTES : A_BYTES;
+          float4* hi = reinterpret_cast<float4*>(base + op * 2 * A_BYTES);
+          float4* lo = reinterpret_cast<float4*>(base + op * 2 * A_BYTES + bytes);
+#pragma unroll 8
+          for (int i = 0; i < bytes / 16 / S::SPLIT_THREADS; ++i) {
+            const int idx = i * S::SPLIT_THREADS + st;
             const float4 v = hi[idx];
-            float4 h, l;
-            h.x = __uint_as_float((__float_as_uint(v.x) + 0x1000u) & 0xFFFFE000u); l.x = v.x - h.x;
-            h.y = __uint_as_float((__float_as_uint(v.y) + 0x1000u) & 0xFFFFE000u); l.y = v.y - h.y;
-            h.z = __uint_as_float((__float_as_uint(v.z) + 0x1000u) & 0xFFFFE000u); l.z = v.z - h.z;
-            h.w = __uint_as_float((__float_as_uint(v.w) + 0x1000u) & 0xFFFFE000u); l.w = v.w - h.w;
-            hi[idx] = h;
+            float4 l;
+            l.x = split_lo(v.x); l.y = split_lo(v.y); l.z = split_lo(v.z); l.w = split_lo(v.w);
             lo[idx] = l;
           }
         }
@@ -243,27 +279,31 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
   } else {
-    // drain warps 6..9: TMEM lane quarter = warp % 4
+    // drain warps: TMEM lane quarter = warp % 4; with wide tiles a second set of four warps takes
+    // the upper 128 columns
+    if (S::TRADE_REGISTERS) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     const int quarter = warp & 3;
+    const int half = (warp - S::FIRST_DRAIN) >> 2;
+    constexpr int DW = 128;               // columns per drain warp
     uint32_t cc = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       int z, m0, n0, k_lo, k_hi;
-      if (!tile_coords(p, item, z, m0, n0, k_lo, k_hi)) continue;
+      if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
       const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
-      const int n_chunks = max(1, (n_stages + p.chunk_stages - 1) / p.chunk_stages);
-      float acc[BN];
+      const int n_chunks = max(1, (n_stages + CHAIN_STAGES - 1) / CHAIN_STAGES);
+      float acc[DW];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < DW; ++i) acc[i] = 0.f;
       for (int ch = 0; ch < n_chunks; ++ch, ++cc) {
         const uint32_t buf = cc & 1u;
         ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (cc >> 1) & 1u, abort_flag, p.status, 205);
         if (!ok) break;
         tc_fence_after();
         if (n_stages > 0) {
-          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * DW;
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = 0; c < DW / 32; ++c) {
             float v[32];
             tmem_ld32(taddr + c * 32, v);
 #pragma unroll
@@ -280,8 +320,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float* out = p.C + (long long)z * p.strideC + (long long)row * p.ldc;
         const float alpha = p.alpha, beta = p.beta;
 #pragma unroll
-        for (int c4 = 0; c4 < BN / 4; ++c4) {
-          const int col = n0 + c4 * 4;
+        for (int c4 = 0; c4 < DW / 4; ++c4) {
+          const int col = n0 + half * DW + c4 * 4;
           if (col + 3 < p.N) {
             float4 o;
             o.x = alpha * acc[c4 * 4 + 0]; o.y = alpha * acc[c4 * 4 + 1];
@@ -310,41 +350,69 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
 }
 
 // rows x K operand.  K-major storage: [rows, K] row-major (ld); MN-major storage: [K, rows].
+// `tile_rows` is the tile's extent along rows (BM for A, BN for B), `bk` its k-extent.
 int make_operand_map(CUtensorMap* map, const float* ptr, bool mn_major, int rows, int K, long long ld,
-                     long long stride_batch, int batch) {
+                     long long stride_batch, int batch, int tile_rows, int bk) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { oc_set_last_error("gemm: cuTensorMapEncodeTiled is not available"); return OC_ERR_CUDA; }
   cuuint64_t dims[3], strides[2];
   cuuint32_t box[3], estr[3] = {1, 1, 1};
-  if (mn_major) { dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K; box[0] = 32; box[1] = BK; }
-  else          { dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; box[0] = BK; box[1] = BM; }
+  if (mn_major) { dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K; box[0] = 32; box[1] = (cuuint32_t)bk; }
+  else          { dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; box[0] = (cuuint32_t)bk; box[1] = (cuuint32_t)tile_rows; }
   dims[2] = (cuuint64_t)batch;
   box[2] = 1;
   strides[0] = (cuuint64_t)ld * 4;
   strides[1] = (cuuint64_t)(batch > 1 ? stride_batch : (long long)dims[1] * ld) * 4;
+  const CUtensorMapSwizzle swz = mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                 : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { oc_set_last_error("gemm: cuTensorMapEncodeTiled failed"); return OC_ERR_CUDA; }
   return OC_OK;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, class S>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcGemmParams& p, int grid, cudaStream_t s) {
-  OC_OPT_IN_SMEM((gemm_tf32x3_kernel<A_MN, B_MN>), SMEM_DYN);
-  gemm_tf32x3_kernel<A_MN, B_MN><<<grid, NUM_THREADS, SMEM_DYN, s>>>(ma, mb, p);
+  OC_OPT_IN_SMEM((gemm_tf32x3_kernel<A_MN, B_MN, S>), S::SMEM_DYN);
+  gemm_tf32x3_kernel<A_MN, B_MN, S><<<grid, S::THREADS, S::SMEM_DYN, s>>>(ma, mb, p);
   OC_CHECK_LAUNCH();
   return OC_OK;
 }
 
 int g_sm_count[OC_MAX_DEVICES] = {};
 int* g_status[OC_MAX_DEVICES] = {};
+int g_tile_shape = 0;   // 0: chosen per product; 1: narrow tiles only; 2: wide tiles wherever allowed
+
+template <class S>
+int launch_shape(const OcGemm& g, int dev, cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  int rc = make_operand_map(&ma, g.A, g.transA != 0, g.M, g.K, g.lda, g.strideA, g.batch, BM, S::BK);
+  if (rc) return rc;
+  rc = make_operand_map(&mb, g.B, g.transB == 0, g.N, g.K, g.ldb, g.strideB, g.batch, S::BN, S::BK);
+  if (rc) return rc;
+  TcGemmParams p{};
+  p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC; p.M = g.M; p.N = g.N; p.K = g.K;
+  p.alpha = g.alpha; p.beta = g.beta; p.flags = g.flags; p.batch = g.batch;
+  p.tiles_m = oc_div_up(g.M, BM); p.tiles_n = oc_div_up(g.N, S::BN);
+  p.status = g_status[dev];
+  const long long items = (long long)p.batch * p.tiles_m * p.tiles_n;
+  OC_REQUIRE(items < (1ll << 30), "gemm: too many tiles");
+  const int grid = (int)((items < g_sm_count[dev]) ? items : g_sm_count[dev]);
+  const bool a_mn = g.transA != 0, b_mn = g.transB == 0;
+  if (a_mn) return b_mn ? launch<true, true, S>(ma, mb, p, grid, stream) : launch<true, false, S>(ma, mb, p, grid, stream);
+  return b_mn ? launch<false, true, S>(ma, mb, p, grid, stream) : launch<false, false, S>(ma, mb, p, grid, stream);
+}
+
+// Relative cost of a wide tile against a narrow one (twice the flops at 1.5 / 2 of the
+// shared-memory traffic per flop).
+constexpr double WIDE_TILE_COST = 1.6;
 
 }  // namespace
 
@@ -361,6 +429,14 @@ bool oc_gemm_tc_eligible(const OcGemm& g) {
          (long long)g.M * g.N >= 64 * 64;
 }
 
+// 0: tile shape chosen per product (default); 1: narrow tiles only; 2: wide tiles for every plain
+// product.  Returns the previous setting.
+extern "C" int oc_set_gemm_tile_shape(int mode) {
+  const int old = g_tile_shape;
+  if (mode >= 0 && mode <= 2) g_tile_shape = mode;
+  return old;
+}
+
 int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   OC_CURRENT_DEVICE(dev);
   if (!g_status[dev]) {
@@ -371,23 +447,20 @@ int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   if (g_sm_count[dev] == 0) {
     OC_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
   }
-  CUtensorMap ma, mb;
-  int rc = make_operand_map(&ma, g.A, g.transA != 0, g.M, g.K, g.lda, g.strideA, g.batch);
-  if (rc) return rc;
-  rc = make_operand_map(&mb, g.B, g.transB == 0, g.N, g.K, g.ldb, g.strideB, g.batch);
-  if (rc) return rc;
-  TcGemmParams p{};
-  p.C = g.C; p.ldc = g.ldc; p.strideC = g.strideC; p.M = g.M; p.N = g.N; p.K = g.K;
-  p.alpha = g.alpha; p.beta = g.beta; p.flags = g.flags; p.batch = g.batch;
-  p.tiles_m = oc_div_up(g.M, BM); p.tiles_n = oc_div_up(g.N, BN);
-  p.chunk_stages = 8;  // 256 k-values (96 MMAs) per accumulation chain
-  p.status = g_status[dev];
-  const long long items = (long long)p.batch * p.tiles_m * p.tiles_n;
-  OC_REQUIRE(items < (1ll << 30), "gemm: too many tiles");
-  const int grid = (int)((items < g_sm_count[dev]) ? items : g_sm_count[dev]);
-  const bool a_mn = g.transA != 0, b_mn = g.transB == 0;
-  if (a_mn) return b_mn ? launch<true, true>(ma, mb, p, grid, stream) : launch<true, false>(ma, mb, p, grid, stream);
-  return b_mn ? launch<false, true>(ma, mb, p, grid, stream) : launch<false, false>(ma, mb, p, grid, stream);
+  // Triangular products (any flag) keep the 128-column tiles their k-ranges and skipped tiles are
+  // defined on.  A plain product takes wide tiles when they need less time, counted in waves
+  // of tiles over the SMs.
+  bool wide = false;
+  if (g.flags == 0 && g_tile_shape != 1) {
+    const long long sms = g_sm_count[dev];
+    const long long tm = oc_div_up(g.M, BM);
+    const long long n_narrow = (long long)g.batch * tm * oc_div_up(g.N, Narrow::BN);
+    const long long n_wide = (long long)g.batch * tm * oc_div_up(g.N, Wide::BN);
+    const double cost_narrow = (double)((n_narrow + sms - 1) / sms);
+    const double cost_wide = WIDE_TILE_COST * (double)((n_wide + sms - 1) / sms);
+    wide = g_tile_shape == 2 || cost_wide < cost_narrow;
+  }
+  return wide ? launch_shape<Wide>(g, dev, stream) : launch_shape<Narrow>(g, dev, stream);
 }
 
 // 0 when no tensor-core GEMM on the current device has recorded an expired wait, else its code.

@@ -800,6 +800,12 @@ def set_gemm_engine(mode: int) -> int:
     return _lib.load().oc_set_gemm_engine(int(mode))
 
 
+def set_gemm_tile_shape(mode: int) -> int:
+    """Output tile of the tensor-core engine for plain products: 0 chosen per product (default),
+    1 always 128 x 128, 2 always 128 x 256.  Returns the previous setting."""
+    return _lib.load().oc_set_gemm_tile_shape(int(mode))
+
+
 def gemm_tc_status() -> int:
     return _lib.load().oc_gemm_tc_status()
 

@@ -62,6 +62,29 @@ def test_gemm_tensor_core_engine(K, ta, tb, m, n, k):
     assert e_tc < 2e-6, (e_tc, e_fma)
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 96), (200, 300, 72), (128, 256, 16), (384, 1000, 520), (4096, 2560, 264)])
+def test_gemm_tile_shapes_give_the_same_bits(K, ta, tb, m, n, k):
+    """128 x 128 and 128 x 256 output tiles cut k into the same accumulation chains, so a plain
+    product does not depend on the shape the engine picks (which depends on M, i.e. on how many
+    rows a rank holds); the last size lets the engine choose wide tiles by itself."""
+    g = torch.Generator().manual_seed(m + 3 * n + 7 * k)
+    a = torch.randn((k, m) if ta else (m, k), generator=g).to(dev())
+    b = torch.randn((n, k) if tb else (k, n), generator=g).to(dev())
+    c0 = torch.randn(m, n, generator=g).to(dev())
+    want = 0.5 * c0.double() + 1.5 * ((a.t() if ta else a).double() @ (b.t() if tb else b).double())
+    out = {}
+    try:
+        for shape in (1, 2, 0):
+            K.set_gemm_tile_shape(shape)
+            out[shape] = K.gemm_f32(a, b, c0.clone(), alpha=1.5, beta=0.5, trans_a=ta, trans_b=tb)
+    finally:
+        K.set_gemm_tile_shape(0)
+    assert K.gemm_tc_status() == 0
+    assert torch.equal(out[1], out[2]) and torch.equal(out[1], out[0])
+    assert ((out[2].double() - want).norm() / want.norm()).item() < 2e-6
+
+
 def test_gemm_tensor_core_long_k_same_sign(K):
     """All-positive operands and K = 8192: the chunked drain keeps the truncation bias of the
     tensor-core accumulator out of the result."""
