@@ -39,8 +39,9 @@ struct Shape {
   static constexpr int BN = BN_, BK = BK_, STAGES = STAGES_, SPLIT_WARPS = 4, FIRST_SPLIT = FIRST_SPLIT_;
   static constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;   // one operand tile (hi or lo)
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);          // A hi, A lo, B hi, B lo
-  static constexpr int SMEM_DYN = STAGES * STAGE_BYTES + 1024;
   static constexpr int DRAIN_WARPS = 4 * (BN / 128);
+  // operand ring, slack for its 1024-byte alignment, 4 KB of epilogue staging per drain warp
+  static constexpr int SMEM_DYN = STAGES * STAGE_BYTES + 1024 + DRAIN_WARPS * 4096;
   static constexpr int FIRST_DRAIN = FIRST_SPLIT + SPLIT_WARPS;
   // With 16 warps the register file gives 128 registers per thread at launch, fewer than a drain
   // thread needs for its 128 partial sums: the warpgroups then trade registers (setmaxnreg).
@@ -315,33 +316,59 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
       }
       if (!ok) break;
-      const int row = m0 + quarter * 32 + lane;
-      if (row < p.M) {
-        float* out = p.C + (long long)z * p.strideC + (long long)row * p.ldc;
-        const float alpha = p.alpha, beta = p.beta;
+      // Epilogue.  A drain thread holds one row of the tile, so writing from the registers would
+      // touch 32 rows per instruction.  Each warp instead passes 32 x 32 slices through 4 KB of
+      // shared memory of its own (16-byte chunks swizzled by row, conflict-free both ways) and
+      // reads / writes C with four full 128-byte row segments per instruction.
+      float4* stg = reinterpret_cast<float4*>(stage_ptr + STAGES * STAGE_BYTES) + (warp - S::FIRST_DRAIN) * 256;
+      float* out_tile = p.C + (long long)z * p.strideC;
+      const float alpha = p.alpha, beta = p.beta;
+      const int sub = lane >> 3, chunk = lane & 7;
 #pragma unroll
-        for (int c4 = 0; c4 < DW / 4; ++c4) {
-          const int col = n0 + half * DW + c4 * 4;
-          if (col + 3 < p.N) {
-            float4 o;
-            o.x = alpha * acc[c4 * 4 + 0]; o.y = alpha * acc[c4 * 4 + 1];
-            o.z = alpha * acc[c4 * 4 + 2]; o.w = alpha * acc[c4 * 4 + 3];
-            if (beta != 0.f) {
-              const float4 old = *reinterpret_cast<const float4*>(out + col);
-              o.x = fmaf(beta, old.x, o.x); o.y = fmaf(beta, old.y, o.y);
-              o.z = fmaf(beta, old.z, o.z); o.w = fmaf(beta, old.w, o.w);
-            }
-            *reinterpret_cast<float4*>(out + col) = o;
-          } else {
+      for (int c = 0; c < DW / 32; ++c) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col + j < p.N) {
-                const float old = (beta != 0.f) ? beta * out[col + j] : 0.f;
-                out[col + j] = fmaf(alpha, acc[c4 * 4 + j], old);
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = alpha * acc[c * 32 + j * 4 + 0]; o.y = alpha * acc[c * 32 + j * 4 + 1];
+          o.z = alpha * acc[c * 32 + j * 4 + 2]; o.w = alpha * acc[c * 32 + j * 4 + 3];
+          stg[lane * 8 + (j ^ (lane & 7))] = o;
+        }
+        __syncwarp();
+        const int col = n0 + half * DW + c * 32 + chunk * 4;
+#pragma unroll
+        for (int i0 = 0; i0 < 8; i0 += 4) {
+          float4 o[4], old[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = (i0 + i) * 4 + sub;
+            const int row = m0 + quarter * 32 + r;
+            o[i] = stg[r * 8 + (chunk ^ (r & 7))];
+            old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (beta != 0.f && row < p.M && col + 3 < p.N)
+              old[i] = *reinterpret_cast<const float4*>(out_tile + (long long)row * p.ldc + col);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = (i0 + i) * 4 + sub;
+            const int row = m0 + quarter * 32 + r;
+            if (row >= p.M) continue;
+            float* out = out_tile + (long long)row * p.ldc + col;
+            if (col + 3 < p.N) {
+              float4 v = o[i];
+              if (beta != 0.f) {
+                v.x = fmaf(beta, old[i].x, v.x); v.y = fmaf(beta, old[i].y, v.y);
+                v.z = fmaf(beta, old[i].z, v.z); v.w = fmaf(beta, old[i].w, v.w);
               }
+              *reinterpret_cast<float4*>(out) = v;
+            } else {
+              const float e[4] = {o[i].x, o[i].y, o[i].z, o[i].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col + j < p.N) out[j] = (beta != 0.f) ? fmaf(beta, out[j], e[j]) : e[j];
             }
           }
         }
+        __syncwarp();
       }
     }
   }
