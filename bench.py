@@ -223,6 +223,16 @@ def run_ours(args):
             host_f = host_q.clone().pin_memory()
             cur_q, cur_f = torch.empty_like(x0), torch.empty_like(x0)
             up, down = torch.cuda.Stream(), torch.cuda.Stream()     # host->device, device->host
+            weights_ready = {}
+
+            def send_weights(j):
+                sent = 0
+                with torch.cuda.stream(up):
+                    for k, v in stack.blocks[j].state_dict().items():
+                        v.copy_(host_blocks[j][k], non_blocking=True)
+                        sent += v.numel() * v.element_size()
+                    weights_ready[j] = up.record_event()
+                return sent
         else:
             cur_q, cur_f = x0.clone(), x0.clone()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -238,21 +248,24 @@ def run_ours(args):
             nxt = stack.blocks[i + 1] if i + 1 < len(stack.blocks) else None
             io = None
             if e2e:
-                # every step starts from host memory (block weights, both activation sets) and ends
-                # with its outputs on the host.  Inside the step the copies run on their own streams,
-                # one chunk of sequences at a time: inputs arrive ahead of the pass that reads them,
-                # outputs leave as soon as they are written.
+                # every step takes its block weights and both activation sets from host memory and
+                # ends with its outputs on the host.  Inside the step the copies run on their own
+                # streams, one chunk of sequences at a time: inputs arrive ahead of the pass that
+                # reads them, outputs leave as soon as they are written.
                 main = torch.cuda.current_stream()
                 up.wait_stream(main)
                 io = HostStreams(main, up, down, host_q, host_f, cur_q, cur_f, chunk=16)
-                with torch.cuda.stream(up):
-                    for k, v in blk.state_dict().items():
-                        v.copy_(host_blocks[i][k], non_blocking=True)
-                        h2d += v.numel() * v.element_size()
-                main.wait_event(up.record_event())
+                if i not in weights_ready:
+                    h2d += send_weights(i)
+                main.wait_event(weights_ready.pop(i))
                 io.start_uploads()
                 h2d += 2 * host_q.numel() * 2
-                nxt = None      # no work is carried across steps in this mode
+                # the next block's pristine weights follow this step's activations on the upload
+                # stream (nothing reads that block before its own step).  The last step sends the
+                # first timed block's weights once more, so that the timed region holds exactly one
+                # weight upload per step.
+                h2d += send_weights(i + 1 if i + 1 < len(stack.blocks) else warmup)
+                nxt = None      # no compute is carried across steps in this mode
             nq, nf = runner.run(blk, cur_q, cur_f, stack.kwargs, next_block=nxt, stream_io=io)
             if args.verbose and rank == 0:
                 st = torch.cuda.memory_stats(dev)
