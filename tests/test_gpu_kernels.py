@@ -63,7 +63,7 @@ def test_gemm_tensor_core_engine(K, ta, tb, m, n, k):
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("m,n,k", [(256, 512, 96), (200, 300, 72), (128, 256, 16), (384, 1000, 520), (4096, 2560, 264)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 96), (200, 300, 72), (128, 256, 16), (384, 1000, 520), (4096, 2560, 264), (300, 200, 64), (64, 136, 24)])
 def test_gemm_tile_shapes_give_the_same_bits(K, ta, tb, m, n, k):
     """128 x 128 and 128 x 256 output tiles cut k into the same accumulation chains, so a plain
     product does not depend on the shape the engine picks (which depends on M, i.e. on how many
