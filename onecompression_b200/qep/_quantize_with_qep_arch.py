@@ -721,7 +721,8 @@ class BlockQuantizer:
             h, c, n = acc.finalize()
             t0 = self._tick(f"pass_quantized+moments[{gi}]", t0)
             if self.dist is not None:
-                h, c, n = self.dist.reduce_moments(h, c, n, fixed_split=True)
+                # the factorisation needs H only: the reduction of C runs beside it
+                h, c, n = self.dist.reduce_moments(h, c, n, fixed_split=True, defer_cross=not self.profile)
                 t0 = self._tick("allreduce", t0)
             factors = {}
             plan = []            # [(modules sharing one call, factor, excluded)]
@@ -750,6 +751,8 @@ class BlockQuantizer:
                 else:
                     plan.append({"key": skey, "modules": [module], "factor": factor, "excluded": excluded,
                                  "child": child})
+            if self.dist is not None:
+                self.dist.wait_cross()
             for entry in plan:
                 mods, excluded = entry["modules"], entry["excluded"]
                 if len(mods) > 1:

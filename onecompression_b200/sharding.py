@@ -47,14 +47,18 @@ class ShardedContext:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self._totals = {}
+        self._pending_cross = None
 
     # ---- tokens -------------------------------------------------------------------
-    def reduce_moments(self, h: torch.Tensor, c: Optional[torch.Tensor], n: int, fixed_split: bool = False):
+    def reduce_moments(self, h: torch.Tensor, c: Optional[torch.Tensor], n: int, fixed_split: bool = False,
+                       defer_cross: bool = False):
         """Per-rank means (2/n_r)·Σ_r → global means (2/N)·Σ.  Returns (h, c, N).
 
         ``fixed_split``: the caller's token split over the ranks does not change between calls with
         the same local count (the calibration sequences of a run), so the global count is
-        exchanged once and remembered, which saves a host synchronisation per call."""
+        exchanged once and remembered, which saves a host synchronisation per call.
+        ``defer_cross``: the reduction of ``c`` is only started; the caller runs what needs ``h``
+        alone (the factorisation) and calls ``wait_cross()`` before it reads ``c``."""
         big_n = self._totals.get(n) if fixed_split else None
         if big_n is None:
             total = torch.tensor([float(n)], dtype=torch.float64, device=h.device)
@@ -67,8 +71,18 @@ class ShardedContext:
         dist.all_reduce(h, group=self.group)
         if c is not None:
             c.mul_(w)
-            dist.all_reduce(c, group=self.group)
+            if defer_cross:
+                self.wait_cross()
+                self._pending_cross = (dist.all_reduce(c, group=self.group, async_op=True), c)
+            else:
+                dist.all_reduce(c, group=self.group)
         return h, c, big_n
+
+    def wait_cross(self):
+        """Make the current stream wait for a cross term whose reduction ``reduce_moments`` started."""
+        pending, self._pending_cross = self._pending_cross, None
+        if pending is not None:
+            pending[0].wait()
 
     # ---- rows ---------------------------------------------------------------------
     def gather_rows(self, local: torch.Tensor, out_features: int, dim: int, per_row: float = 1.0,

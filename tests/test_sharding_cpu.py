@@ -61,6 +61,12 @@ def _worker(rank, world, port, out_dir):
     h_all, c_all, n_all = orc.hessian_and_crossterm([xq], [xf])
     assert n == n_all
     assert torch.allclose(h, h_all, rtol=1e-5, atol=1e-6) and torch.allclose(c, c_all, rtol=1e-4, atol=1e-6)
+    # the cross term reduced in the background while the caller works on H: same values after the wait
+    h2, c2, n2 = ctx.reduce_moments(h_loc.clone(), c_loc.clone(), n_loc, defer_cross=True)
+    assert torch.equal(h2, h) and n2 == n
+    ctx.wait_cross()
+    assert torch.equal(c2, c)
+    ctx.wait_cross()                      # nothing pending: a no-op
 
     # rows: every rank quantizes its slab with the oracle standing in for the kernels
     u = orc.inverse_hessian_upper(h_all.clone(), 0.01)
