@@ -104,6 +104,23 @@ class ShardedContext:
         dist.all_gather(parts, padded.contiguous(), group=self.group)
         return torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
 
+    def gather_column_slabs(self, slabs):
+        """Several 2-D results whose columns are split evenly over the ranks ([R_i, cols_i] here,
+        [R_i, cols_i * world] assembled), moved by ONE all-gather of their bytes instead of one
+        collective (and its padding, list and concatenation) each.  Returns the assembled tensors."""
+        flat = torch.cat([t.contiguous().reshape(-1).view(torch.uint8) for t in slabs])
+        everyone = torch.empty(self.world * flat.numel(), dtype=torch.uint8, device=flat.device)
+        dist.all_gather_into_tensor(everyone, flat, group=self.group)
+        everyone = everyone.view(self.world, flat.numel())
+        out, off = [], 0
+        for t in slabs:
+            nbytes = t.numel() * t.element_size()
+            part = everyone[:, off:off + nbytes].contiguous().view(t.dtype)
+            out.append(part.reshape(self.world, t.shape[0], t.shape[1]).permute(1, 0, 2)
+                       .reshape(t.shape[0], self.world * t.shape[1]))
+            off += nbytes
+        return out
+
     def quantize_rows(self, quantizer, module, h, c, cfg, factor,
                       compute: Optional[Callable] = None):
         """Correct and quantize this rank's row slab of ``module`` and assemble the full
@@ -181,7 +198,11 @@ class ShardedContext:
             local = compute(slab, c)
             w_hat = self.gather_rows(local["dequantized"], out_features, dim=0)
         packed = "qweight" in local
-        if packed:
+        if packed and out_features % (32 * self.world) == 0:
+            # equal slabs: the three column-split results travel in one collective
+            qweight, qzeros, scales = self.gather_column_slabs(
+                [local["qweight"], local["qzeros"], local["scales"]])
+        elif packed:
             qweight = self.gather_rows(local["qweight"], out_features, dim=1)
             qzeros = self.gather_rows(local["qzeros"], out_features, dim=1, per_row=bits / 32.0)
         else:
@@ -189,7 +210,8 @@ class ShardedContext:
             # [rows, in] and raw zero points [G, rows], as on one GPU
             qweight = self.gather_rows(local["codes"], out_features, dim=0)
             qzeros = self.gather_rows(local["zeros"], out_features, dim=1)
-        scales = self.gather_rows(local["scales"], out_features, dim=1)
+        if not (packed and out_features % (32 * self.world) == 0):
+            scales = self.gather_rows(local["scales"], out_features, dim=1)
         perm = getattr(factor, "perm", None) if quantizer.actorder else None
         pieces, r0 = [], 0
         for r in rows:
