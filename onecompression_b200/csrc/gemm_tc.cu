@@ -20,8 +20,7 @@
 // and 8 drain warps.  The kernel is bound by shared-memory bandwidth (TMA write, split read
 // and two writes, three operand reads per MMA pair); per flop a wide tile reads the operands
 // 1.5 instead of 2 times, so it is chosen when the product has enough tiles to fill the SMs.
-// Both shapes cut k into the same 256-wide chains, so a plain product gives the same bits
-// with either.
+// Both shapes cut k into the same chains, so a product gives the same bits with either.
 // Operands may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major); both are
 // native tcgen05 layouts, so the four transpose combinations need no data movement.
 // All mbarrier waits are bounded (see tc_common.cuh).
@@ -141,6 +140,13 @@ __device__ __forceinline__ bool tile_coords(const TcGemmParams& p, int item, int
   return true;
 }
 
+// A wide tile of a lower-tiles-only product that straddles the diagonal: its upper 128 columns are
+// a tile the narrow shape would skip, so they get no MMA and are not written.
+template <int BN>
+__device__ __forceinline__ bool upper_half_in_use(const TcGemmParams& p, int m0, int n0) {
+  return BN == 128 || !(p.flags & OC_GEMM_SKIP_UPPER_TILES) || n0 + 128 <= m0 + BM - 1;
+}
+
 template <bool A_MN, bool B_MN, class S>
 __global__ void __launch_bounds__(S::THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -208,12 +214,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t ID = idesc<A_MN, B_MN, BN>();
+      constexpr uint32_t ID_FULL = idesc<A_MN, B_MN, BN>(), ID_HALF = idesc<A_MN, B_MN, 128>();
       uint32_t stage = 0, phase = 0, cc = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         int z, m0, n0, k_lo, k_hi;
         if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
+        const uint32_t ID = upper_half_in_use<BN>(p, m0, n0) ? ID_FULL : ID_HALF;
         const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
         const int n_chunks = max(1, (n_stages + CHAIN_STAGES - 1) / CHAIN_STAGES);
         for (int ch = 0; ch < n_chunks && ok; ++ch, ++cc) {
@@ -293,6 +300,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (!tile_coords<BN, BK>(p, item, z, m0, n0, k_lo, k_hi)) continue;
       const int n_stages = max(0, (k_hi - k_lo + BK - 1) / BK);
       const int n_chunks = max(1, (n_stages + CHAIN_STAGES - 1) / CHAIN_STAGES);
+      const bool in_use = half == 0 || upper_half_in_use<BN>(p, m0, n0);
       float acc[DW];
 #pragma unroll
       for (int i = 0; i < DW; ++i) acc[i] = 0.f;
@@ -301,7 +309,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         ok = mbar_wait(smem_u32(&bar_acc_full[buf]), (cc >> 1) & 1u, abort_flag, p.status, 205);
         if (!ok) break;
         tc_fence_after();
-        if (n_stages > 0) {
+        if (n_stages > 0 && in_use) {
           const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + half * DW;
 #pragma unroll
           for (int c = 0; c < DW / 32; ++c) {
@@ -316,6 +324,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
       }
       if (!ok) break;
+      if (!in_use) continue;
       // Epilogue.  A drain thread holds one row of the tile, so writing from the registers would
       // touch 32 rows per instruction.  Each warp instead passes 32 x 32 slices through 4 KB of
       // shared memory of its own (16-byte chunks swizzled by row, conflict-free both ways) and
@@ -474,15 +483,23 @@ int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   if (g_sm_count[dev] == 0) {
     OC_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
   }
-  // Triangular products (any flag) keep the 128-column tiles their k-ranges and skipped tiles are
-  // defined on.  A plain product takes wide tiles when they need less time, counted in waves
-  // of tiles over the SMs.
+  // Products with k-range flags keep the 128-column tiles those ranges are defined on.  A plain
+  // product, or one that only skips the tiles above the diagonal, takes wide tiles when they need
+  // less time, counted in waves of tiles over the SMs.
   bool wide = false;
-  if (g.flags == 0 && g_tile_shape != 1) {
+  if ((g.flags == 0 || g.flags == OC_GEMM_SKIP_UPPER_TILES) && g_tile_shape != 1) {
     const long long sms = g_sm_count[dev];
     const long long tm = oc_div_up(g.M, BM);
-    const long long n_narrow = (long long)g.batch * tm * oc_div_up(g.N, Narrow::BN);
-    const long long n_wide = (long long)g.batch * tm * oc_div_up(g.N, Wide::BN);
+    const long long tn_narrow = oc_div_up(g.N, Narrow::BN), tn_wide = oc_div_up(g.N, Wide::BN);
+    long long n_narrow = tm * tn_narrow, n_wide = tm * tn_wide;
+    if (g.flags == OC_GEMM_SKIP_UPPER_TILES) {
+      n_narrow = n_wide = 0;
+      for (long long i = 0; i < tm; ++i) {      // tiles of row block i that reach the diagonal or lie below it
+        n_narrow += (i + 1 < tn_narrow) ? i + 1 : tn_narrow;
+        n_wide += (i / 2 + 1 < tn_wide) ? i / 2 + 1 : tn_wide;
+      }
+    }
+    n_narrow *= g.batch; n_wide *= g.batch;
     const double cost_narrow = (double)((n_narrow + sms - 1) / sms);
     const double cost_wide = WIDE_TILE_COST * (double)((n_wide + sms - 1) / sms);
     wide = g_tile_shape == 2 || cost_wide < cost_narrow;

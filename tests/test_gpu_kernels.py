@@ -85,6 +85,32 @@ def test_gemm_tile_shapes_give_the_same_bits(K, ta, tb, m, n, k):
     assert ((out[2].double() - want).norm() / want.norm()).item() < 2e-6
 
 
+@pytest.mark.parametrize("n,k", [(1024, 160), (1152, 512), (640, 48)])
+def test_gemm_lower_tiles_only_with_wide_tiles(K, n, k):
+    """Symmetric rank-k update that skips the 128 x 128 tiles above the diagonal (flag 1): a wide
+    tile that straddles the diagonal computes and writes only its lower 128 columns, so the result
+    and the untouched tiles are those of the narrow shape, bit for bit."""
+    g = torch.Generator().manual_seed(n + k)
+    p = torch.randn(n, k, generator=g).to(dev())
+    c0 = torch.randn(n, n, generator=g).to(dev())
+    out = {}
+    try:
+        for shape in (1, 2):
+            K.set_gemm_tile_shape(shape)
+            out[shape] = K.gemm_f32(p, p, c0.clone(), alpha=-1.0, beta=1.0, trans_b=True, flags=1)
+    finally:
+        K.set_gemm_tile_shape(0)
+    assert K.gemm_tc_status() == 0
+    assert torch.equal(out[1], out[2])
+    want = c0.double() - p.double() @ p.double().t()
+    low = torch.tril(torch.ones(n, n, device=dev(), dtype=torch.bool))
+    assert ((out[2].double() - want)[low].norm() / want[low].norm()).item() < 2e-6
+    # tiles strictly above the diagonal were skipped: C is unchanged there
+    blk = torch.arange(n, device=dev()) // 128
+    above = blk[None, :] > blk[:, None]
+    assert torch.equal(out[2][above], c0[above])
+
+
 def test_gemm_tensor_core_long_k_same_sign(K):
     """All-positive operands and K = 8192: the chunked drain keeps the truncation bias of the
     tensor-core accumulator out of the result."""
