@@ -483,16 +483,17 @@ int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   if (g_sm_count[dev] == 0) {
     OC_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
   }
-  // Products with k-range flags keep the 128-column tiles those ranges are defined on.  A plain
-  // product, or one that only skips the tiles above the diagonal, takes wide tiles when they need
-  // less time, counted in waves of tiles over the SMs.
+  // Either tile shape serves every product: the k-range flags state that the operand IS zero
+  // outside the range, so a wide tile only multiplies a few more exact zeros (its k-range is the
+  // union of its two halves' ranges, and the chains of both shapes start on the same 128-grid).
+  // Wide tiles are taken when they need less time, counted in waves of tiles over the SMs.
   bool wide = false;
-  if ((g.flags == 0 || g.flags == OC_GEMM_SKIP_UPPER_TILES) && g_tile_shape != 1) {
+  if (g_tile_shape != 1) {
     const long long sms = g_sm_count[dev];
     const long long tm = oc_div_up(g.M, BM);
     const long long tn_narrow = oc_div_up(g.N, Narrow::BN), tn_wide = oc_div_up(g.N, Wide::BN);
     long long n_narrow = tm * tn_narrow, n_wide = tm * tn_wide;
-    if (g.flags == OC_GEMM_SKIP_UPPER_TILES) {
+    if (g.flags & OC_GEMM_SKIP_UPPER_TILES) {
       n_narrow = n_wide = 0;
       for (long long i = 0; i < tm; ++i) {      // tiles of row block i that reach the diagonal or lie below it
         n_narrow += (i + 1 < tn_narrow) ? i + 1 : tn_narrow;

@@ -111,6 +111,31 @@ def test_gemm_lower_tiles_only_with_wide_tiles(K, n, k):
     assert torch.equal(out[2][above], c0[above])
 
 
+@pytest.mark.parametrize("flag", [2, 8, 4, 16])
+def test_gemm_triangular_ranges_with_wide_tiles(K, flag):
+    """The k-range flags with 128 x 256 tiles: a wide tile runs the union of its halves' ranges, i.e.
+    a few more exact zeros of the triangular operand, and gives the bits of the narrow shape."""
+    g = torch.Generator().manual_seed(flag)
+    n, m = 1152, 520
+    tri = torch.randn(n, n, generator=g)
+    tri = torch.tril(tri) if flag in (2, 4) else torch.triu(tri)
+    other = torch.randn(m, n, generator=g)
+    if flag in (2, 8):                       # B triangular: C = other @ tri
+        a, b, want = other, tri, other.double() @ tri.double()
+    else:                                    # A triangular: C = tri @ other^T
+        a, b, want = tri, other.t().contiguous(), tri.double() @ other.double().t()
+    out = {}
+    try:
+        for shape in (1, 2):
+            K.set_gemm_tile_shape(shape)
+            out[shape] = K.gemm_f32(a.to(dev()), b.to(dev()), flags=flag)
+    finally:
+        K.set_gemm_tile_shape(0)
+    assert K.gemm_tc_status() == 0
+    assert torch.equal(out[1], out[2])
+    assert ((out[2].cpu().double() - want).norm() / want.norm()).item() < 2e-6
+
+
 def test_gemm_tensor_core_long_k_same_sign(K):
     """All-positive operands and K = 8192: the chunked drain keeps the truncation bias of the
     tensor-core accumulator out of the result."""
