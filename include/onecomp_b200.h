@@ -258,6 +258,10 @@ int oc_gemm_tc_status(void);
  * 128x128, 2 forces 128x256.  Both cut k into the same accumulation chains, so the result bits do
  * not depend on the choice.  Returns the previous setting. */
 int oc_set_gemm_tile_shape(int mode);
+/* The shape oc_set_gemm_tile_shape(0) gives a product of M x N (x batch) with `flags` on a device
+ * with `sms` SMs: 1 = 128x128, 2 = 128x256 (fewer waves of tiles, a wide tile counted as 1.6 narrow
+ * ones; lower-tiles-only products count the tiles that reach the diagonal).  Host arithmetic only. */
+int oc_gemm_tile_choice(int M, int N, int batch, int flags, int sms);
 
 #ifdef __cplusplus
 }

@@ -45,6 +45,7 @@ SIGNATURES = {
     "oc_gemm_f32": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _F, _I, _I, _I, _P]),
     "oc_set_gemm_engine": (_I, [_I]),
     "oc_set_gemm_tile_shape": (_I, [_I]),
+    "oc_gemm_tile_choice": (_I, [_I, _I, _I, _I, _I]),
     "oc_gemm_tc_status": (_I, []),
 }
 

@@ -473,6 +473,30 @@ extern "C" int oc_set_gemm_tile_shape(int mode) {
   return old;
 }
 
+// The tile shape a product gets: 1 = 128 x 128, 2 = 128 x 256.  Host arithmetic only.
+// Either shape serves every product: the k-range flags state that the operand IS zero outside the
+// range, so a wide tile only multiplies a few more exact zeros (its k-range is the union of its two
+// halves' ranges, and the chains of both shapes start on the same 128-grid).  Wide tiles are taken
+// when they need less time, counted in waves of tiles over `sms` SMs.
+extern "C" int oc_gemm_tile_choice(int M, int N, int batch, int flags, int sms) {
+  if (g_tile_shape == 1 || g_tile_shape == 2) return g_tile_shape;
+  if (M <= 0 || N <= 0 || batch <= 0 || sms <= 0) return 1;
+  const long long tm = oc_div_up(M, BM);
+  const long long tn_narrow = oc_div_up(N, Narrow::BN), tn_wide = oc_div_up(N, Wide::BN);
+  long long n_narrow = tm * tn_narrow, n_wide = tm * tn_wide;
+  if (flags & OC_GEMM_SKIP_UPPER_TILES) {
+    n_narrow = n_wide = 0;
+    for (long long i = 0; i < tm; ++i) {      // tiles of row block i that reach the diagonal or lie below it
+      n_narrow += (i + 1 < tn_narrow) ? i + 1 : tn_narrow;
+      n_wide += (i / 2 + 1 < tn_wide) ? i / 2 + 1 : tn_wide;
+    }
+  }
+  n_narrow *= batch; n_wide *= batch;
+  const double cost_narrow = (double)((n_narrow + sms - 1) / sms);
+  const double cost_wide = WIDE_TILE_COST * (double)((n_wide + sms - 1) / sms);
+  return cost_wide < cost_narrow ? 2 : 1;
+}
+
 int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   OC_CURRENT_DEVICE(dev);
   if (!g_status[dev]) {
@@ -483,28 +507,7 @@ int oc_gemm_tc_launch(const OcGemm& g, cudaStream_t stream) {
   if (g_sm_count[dev] == 0) {
     OC_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
   }
-  // Either tile shape serves every product: the k-range flags state that the operand IS zero
-  // outside the range, so a wide tile only multiplies a few more exact zeros (its k-range is the
-  // union of its two halves' ranges, and the chains of both shapes start on the same 128-grid).
-  // Wide tiles are taken when they need less time, counted in waves of tiles over the SMs.
-  bool wide = false;
-  if (g_tile_shape != 1) {
-    const long long sms = g_sm_count[dev];
-    const long long tm = oc_div_up(g.M, BM);
-    const long long tn_narrow = oc_div_up(g.N, Narrow::BN), tn_wide = oc_div_up(g.N, Wide::BN);
-    long long n_narrow = tm * tn_narrow, n_wide = tm * tn_wide;
-    if (g.flags & OC_GEMM_SKIP_UPPER_TILES) {
-      n_narrow = n_wide = 0;
-      for (long long i = 0; i < tm; ++i) {      // tiles of row block i that reach the diagonal or lie below it
-        n_narrow += (i + 1 < tn_narrow) ? i + 1 : tn_narrow;
-        n_wide += (i / 2 + 1 < tn_wide) ? i / 2 + 1 : tn_wide;
-      }
-    }
-    n_narrow *= g.batch; n_wide *= g.batch;
-    const double cost_narrow = (double)((n_narrow + sms - 1) / sms);
-    const double cost_wide = WIDE_TILE_COST * (double)((n_wide + sms - 1) / sms);
-    wide = g_tile_shape == 2 || cost_wide < cost_narrow;
-  }
+  const bool wide = oc_gemm_tile_choice(g.M, g.N, g.batch, g.flags, g_sm_count[dev]) == 2;
   return wide ? launch_shape<Wide>(g, dev, stream) : launch_shape<Narrow>(g, dev, stream);
 }
 
